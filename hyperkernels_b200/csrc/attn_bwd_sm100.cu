@@ -1,0 +1,390 @@
+// attn_bwd_sm100.cu -- fused attention backward for sm_100a.
+//
+// Computes what mem_efficient_bwd_unified_kernel_exp12<64,Causal> computes
+// (kernels/attention/mem_efficient_bwd_unified_kernel_exp12.cu:54-329 of the
+// reference), one KV tile per CTA, looping over the query tiles that can see it:
+//   S = Q K^T, dP = dO V^T                    (:186-212)
+//   p = exp2(log2e * (S*scale - LSE)), 0 outside bounds / above the diagonal   (:224-227)
+//   dS = p * (dP - D) * scale                 (:228)
+//   dQ_i += dS K_j   (accumulated into global memory with atomics, :239-282)
+//   dK_j += dS^T Q_i (:261-274)     dV_j += P^T dO_i (:285-299)
+// plus the dropout keep-mask (p is multiplied by it), which the reference
+// backward lacks but its forward implies.
+//
+// Blackwell structure (one CTA = one 128-row KV tile, 128-row query tiles):
+// the transposed products S^T = K Q^T and dP^T = V dO^T put key rows on the 128
+// tensor-memory lanes, so P^T and dS^T -- written back over S^T and dP^T by the
+// compute warps -- are directly the tensor-memory A operands of dV += P^T dO and
+// dK += dS^T Q.  dS is also staged once through shared memory (MN-major) as the
+// A operand of dQ = dS K.  dV, dK (64 columns each) stay in tensor memory for
+// the whole CTA; dQ (64 columns) is drained per query tile with vectorised fp32
+// reductions.
+//
+// Q, dO and K each feed one product that contracts over d (K-major operand,
+// 16-byte-chunk swizzle) and one that contracts over the sequence (MN-major
+// operand, which for TF32 must use the 32-byte-chunk swizzle), so TMA brings
+// each of them into shared memory twice, once per swizzle.  The K-major copies
+// of Q and dO are dead once S^T and dP^T are done, and dS is staged over them.
+//   warp 0     TMA producer (K, V once; Q and dO per query tile)
+//   warp 1     MMA issuer
+//   warps 2-5  compute: thread r owns key row r (tensor-memory lane r)
+#include "attn_kernels.cuh"
+#include "philox.h"
+
+namespace hk {
+
+namespace bwd {
+
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int COL_S = 0;     // S^T, then P^T
+constexpr int COL_DP = 128;  // dP^T, then dS^T
+constexpr int COL_DV = 256;
+constexpr int COL_DK = 320;
+constexpr int COL_DQ = 384;
+
+struct __align__(16) Shared {
+    float lse[TILE];   // LSE * log2e of the current query tile (+inf for rows past the end)
+    float dsum[TILE];  // D of the current query tile
+    uint64_t kv_full, qdo_full, qdo_empty, s_full, ds_ready, dq_full, dq_empty, staged;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+constexpr int OFF_KK = 0;                // K, K-major swizzle   (S^T = K Q^T)
+constexpr int OFF_KM = TILE_BYTES;       // K, MN-major swizzle  (dQ = dS K)
+constexpr int OFF_V = 2 * TILE_BYTES;    // V, K-major           (dP^T = V dO^T)
+constexpr int OFF_QK = 3 * TILE_BYTES;   // Q, K-major           (S^T)      } dS staging, 4 boxes of
+constexpr int OFF_DOK = 4 * TILE_BYTES;  // dO, K-major          (dP^T)     } [128 kv][32 q], overlays these two
+constexpr int OFF_DS = OFF_QK;
+constexpr int OFF_QM = 5 * TILE_BYTES;   // Q, MN-major          (dK += dS^T Q)
+constexpr int OFF_DOM = 6 * TILE_BYTES;  // dO, MN-major         (dV += P^T dO)
+constexpr int OFF_SH = 7 * TILE_BYTES;
+constexpr int SMEM_BYTES = OFF_SH + sizeof(Shared) + 1024;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may opt in to");
+
+enum WaitId { W_KVFULL = 201, W_QDOFULL, W_QDOEMPTY, W_SFULL, W_DSREADY, W_DQFULL, W_DQEMPTY, W_STAGED };
+
+}  // namespace bwd
+
+__global__ void __launch_bounds__(bwd::NUM_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapdO,
+                const __grid_constant__ CUtensorMap mapQm, const __grid_constant__ CUtensorMap mapKm,
+                const __grid_constant__ CUtensorMap mapdOm, const BwdArgs a) {
+    using namespace bwd;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sK = smem + OFF_KK;
+    uint8_t* sKm = smem + OFF_KM;
+    uint8_t* sV = smem + OFF_V;
+    uint8_t* sQ = smem + OFF_QK;
+    uint8_t* sdO = smem + OFF_DOK;
+    uint8_t* sQm = smem + OFF_QM;
+    uint8_t* sdOm = smem + OFF_DOM;
+    uint8_t* sdS = smem + OFF_DS;
+    Shared& sh = *reinterpret_cast<Shared*>(smem + OFF_SH);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // early KV tiles first: under the causal mask they see the most query tiles
+    const int bh = blockIdx.x % a.BH;
+    const int kt = (int)(blockIdx.x / a.BH);
+    const int b = bh / a.H;
+    const int h = bh - b * a.H;
+    const int kv0 = kt * TILE;
+    const int n_qtiles = (a.Tq + TILE - 1) / TILE;
+
+    // first query tile with a row at or below the diagonal of this KV tile
+    int it0 = 0;
+    if (a.causal) {
+        const long long first_q = (long long)kv0 + a.k_pos0 - a.q_pos0;  // smallest local q that sees key kv0
+        if (first_q > 0) it0 = (int)min((long long)n_qtiles, first_q / TILE);
+    }
+    const int n_it = n_qtiles - it0;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sh.kv_full, 1);
+        mbar_init(&sh.qdo_full, 1);
+        mbar_init(&sh.qdo_empty, 1);
+        mbar_init(&sh.s_full, 1);
+        mbar_init(&sh.ds_ready, 128);
+        mbar_init(&sh.dq_full, 1);
+        mbar_init(&sh.dq_empty, 128);
+        mbar_init(&sh.staged, 128);
+        sh.abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(&sh.tmem_base, TMEM_COLS);
+        tmem_relinquish();
+        tc_fence_before_sync();
+    }
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sh.tmem_base;
+    WaitCtx wc{&sh.abort_flag, a.status};
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0 && n_it > 0) {
+            tma_prefetch_desc(&mapQ);
+            tma_prefetch_desc(&mapK);
+            tma_prefetch_desc(&mapV);
+            tma_prefetch_desc(&mapdO);
+            tma_prefetch_desc(&mapQm);
+            tma_prefetch_desc(&mapKm);
+            tma_prefetch_desc(&mapdOm);
+            mbar_arrive_expect_tx(&sh.kv_full, 3 * TILE_BYTES);
+            tma_load_4d(sK, &mapK, &sh.kv_full, 0, kv0, h, b);
+            tma_load_4d(sK + BOX_BYTES, &mapK, &sh.kv_full, HALF_D, kv0, h, b);
+            tma_load_4d(sKm, &mapKm, &sh.kv_full, 0, kv0, h, b);
+            tma_load_4d(sKm + BOX_BYTES, &mapKm, &sh.kv_full, HALF_D, kv0, h, b);
+            tma_load_4d(sV, &mapV, &sh.kv_full, 0, kv0, h, b);
+            tma_load_4d(sV + BOX_BYTES, &mapV, &sh.kv_full, HALF_D, kv0, h, b);
+            int issued = 0;
+            for (int it = 0; it < n_it; ++it) {
+                if (it > 0 && !mbar_wait(wc, &sh.qdo_empty, (it - 1) & 1, W_QDOEMPTY, it)) break;
+                const int q0 = (it0 + it) * TILE;
+                mbar_arrive_expect_tx(&sh.qdo_full, 4 * TILE_BYTES);
+                tma_load_4d(sQ, &mapQ, &sh.qdo_full, 0, q0, h, b);
+                tma_load_4d(sQ + BOX_BYTES, &mapQ, &sh.qdo_full, HALF_D, q0, h, b);
+                tma_load_4d(sdO, &mapdO, &sh.qdo_full, 0, q0, h, b);
+                tma_load_4d(sdO + BOX_BYTES, &mapdO, &sh.qdo_full, HALF_D, q0, h, b);
+                tma_load_4d(sQm, &mapQm, &sh.qdo_full, 0, q0, h, b);
+                tma_load_4d(sQm + BOX_BYTES, &mapQm, &sh.qdo_full, HALF_D, q0, h, b);
+                tma_load_4d(sdOm, &mapdOm, &sh.qdo_full, 0, q0, h, b);
+                tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qdo_full, HALF_D, q0, h, b);
+                issued = it + 1;
+            }
+            // Do not leave the CTA while bulk copies into its shared memory are in flight.
+            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.kv_full, 0); ++i) {}
+            if (issued > 0)
+                for (int i = 0; i < 100000 && !mbar_try_wait(&sh.qdo_full, (issued - 1) & 1); ++i) {}
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0 && n_it > 0) {
+            constexpr uint32_t IDESC_ST = make_idesc_tf32(TILE, TILE, false, false);     // K-major x K-major, N = 128
+            constexpr uint32_t IDESC_TS = make_idesc_tf32(TILE, HEAD_DIM, false, true);  // tmem A, MN-major B, N = 64
+            constexpr uint32_t IDESC_DQ = make_idesc_tf32(TILE, HEAD_DIM, true, true);   // MN-major A and B, N = 64
+            const uint32_t k_addr = smem_u32(sK), km_addr = smem_u32(sKm), v_addr = smem_u32(sV), q_addr = smem_u32(sQ),
+                           do_addr = smem_u32(sdO), qm_addr = smem_u32(sQm), dom_addr = smem_u32(sdOm),
+                           ds_addr = smem_u32(sdS);
+            bool ok = mbar_wait(wc, &sh.kv_full, 0, W_KVFULL);
+            for (int it = 0; ok && it < n_it; ++it) {
+                const uint32_t par = it & 1;
+                if (!(ok = mbar_wait(wc, &sh.qdo_full, par, W_QDOFULL, it))) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // S^T = K Q^T
+                    umma_ss_tf32(tmem + COL_S, kmajor_desc(k_addr, kk, BOX_BYTES), kmajor_desc(q_addr, kk, BOX_BYTES),
+                                 IDESC_ST, kk > 0);
+#pragma unroll
+                for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // dP^T = V dO^T
+                    umma_ss_tf32(tmem + COL_DP, kmajor_desc(v_addr, kk, BOX_BYTES), kmajor_desc(do_addr, kk, BOX_BYTES),
+                                 IDESC_ST, kk > 0);
+                umma_commit(&sh.s_full);
+                if (!(ok = mbar_wait(wc, &sh.ds_ready, par, W_DSREADY, it))) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < TILE / 8; ++kk)  // dV += P^T dO
+                    umma_ts_tf32(tmem + COL_DV, tmem + COL_S + kk * 8, mnmajor_desc(dom_addr, kk, BOX_BYTES), IDESC_TS,
+                                 (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < TILE / 8; ++kk)  // dK += dS^T Q
+                    umma_ts_tf32(tmem + COL_DK, tmem + COL_DP + kk * 8, mnmajor_desc(qm_addr, kk, BOX_BYTES), IDESC_TS,
+                                 (it > 0 || kk > 0) ? 1u : 0u);
+                if (it > 0 && !(ok = mbar_wait(wc, &sh.dq_empty, (it - 1) & 1, W_DQEMPTY, it))) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < TILE / 8; ++kk)  // dQ = dS K
+                    umma_ss_tf32(tmem + COL_DQ, mnmajor_desc(ds_addr, kk, BOX_BYTES), mnmajor_desc(km_addr, kk, BOX_BYTES),
+                                 IDESC_DQ, kk > 0);
+                umma_commit(&sh.qdo_empty);
+                umma_commit(&sh.dq_full);
+            }
+        }
+    } else {
+        // ------------------------------ compute ------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;  // key row inside the tile = tensor-memory lane
+        const int tid = (warp - 2) * 32 + lane;  // 0..127 among the compute warps
+        const int kvrow = kv0 + row;
+        const bool kv_ok = kvrow < a.Tk;
+        const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
+        const float* lse_bh = a.LSE + (int64_t)b * a.lse_sB + (int64_t)h * a.lse_sH;
+        const float* d_bh = a.D + (int64_t)b * a.d_sB + (int64_t)h * a.d_sH;
+        float* dq_bh = a.dQ + (int64_t)b * a.dq_sB + (int64_t)h * a.dq_sH;
+        bool ok = true;
+        uint32_t rs[32], rp[32];
+
+        for (int it = 0; it < n_it; ++it) {
+            const int q0 = (it0 + it) * TILE;
+            {
+                const int q = q0 + tid;
+                float L = INFINITY, Dv = 0.f;
+                if (q < a.Tq) {
+                    const float l = __ldg(lse_bh + q);
+                    L = (l == -INFINITY) ? INFINITY : l * LOG2E;  // fully dropped row: every p is 0
+                    Dv = __ldg(d_bh + q);
+                }
+                // safe to overwrite: every compute thread finished reading the previous
+                // tile's values before ds_ready, which the dq_full waited on above follows
+                sh.lse[tid] = L;
+                sh.dsum[tid] = Dv;
+            }
+            // an mbarrier rather than bar.sync: its wait is bounded, so a CTA that is
+            // winding down after a failed wait cannot strand warps at a barrier
+            mbar_arrive(&sh.staged);
+            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.staged, it & 1, W_STAGED, it));
+            if (!ok) break;
+            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.s_full, it & 1, W_SFULL, it));
+            if (!ok) break;
+            tc_fence_after_sync();
+
+            // first query column (local to the tile) this key row is visible to
+            int cmin = 0;
+            if (a.causal) {
+                const long long c = (long long)a.k_pos0 + kvrow - a.q_pos0 - q0;
+                cmin = (int)max(0ll, min((long long)TILE, c));
+            }
+            if (!kv_ok) cmin = TILE;
+
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(trow + COL_S + c * 32, rs);
+                tmem_ld32(trow + COL_DP + c * 32, rp);
+                tmem_wait_ld();
+                uint32_t keep = 0xffffffffu;
+                if (a.dropout_mode == 2) {
+                    keep = 0u;
+                    const uint32_t kpos = (uint32_t)(a.k_pos0 + kvrow);
+#pragma unroll 4
+                    for (int i = 0; i < 32; ++i) {
+                        hk_philox4_t w = hk_philox_row4(a.seed, a.offset, (uint32_t)bh,
+                                                        (uint32_t)(a.q_pos0 + q0 + c * 32 + i), kpos >> 2);
+                        const uint32_t word = (kpos & 3u) == 0 ? w.v[0] : (kpos & 3u) == 1 ? w.v[1]
+                                              : (kpos & 3u) == 2 ? w.v[2] : w.v[3];
+                        keep |= (word >= a.drop_thr ? 1u : 0u) << i;
+                    }
+                } else if (a.dropout_mode == 1) {
+                    keep = 0u;
+                    if (kv_ok) {
+#pragma unroll 4
+                        for (int i = 0; i < 32; ++i) {
+                            const int q = q0 + c * 32 + i;
+                            if (q < a.Tq && __ldg(a.mask + ((size_t)bh * a.Tq + q) * (size_t)a.Tk + kvrow) != 0.f)
+                                keep |= 1u << i;
+                        }
+                    }
+                }
+                uint32_t ds_bits[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int cc = c * 32 + i;
+                    float p = ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -sh.lse[cc]));
+                    if (cc < cmin || !((keep >> i) & 1u)) p = 0.f;
+                    const float ds = p * (__uint_as_float(rp[i]) - sh.dsum[cc]) * a.scale;
+                    rs[i] = tf32_round_bits(__float_as_uint(p));
+                    ds_bits[i] = tf32_round_bits(__float_as_uint(ds));
+                }
+                tmem_st32(trow + COL_S + c * 32, rs);
+                tmem_st32(trow + COL_DP + c * 32, ds_bits);
+                // dS into shared memory (MN-major A operand of dQ = dS K): box c holds query
+                // columns 32c..32c+31, one 128-byte row per key row, 32-byte chunks
+                // XOR-swizzled with (row & 3)
+                uint8_t* drow = sdS + c * BOX_BYTES + row * 128;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    uint4 v = make_uint4(ds_bits[4 * t], ds_bits[4 * t + 1], ds_bits[4 * t + 2], ds_bits[4 * t + 3]);
+                    *reinterpret_cast<uint4*>(drow + ((((t >> 1) ^ (row & 3)) << 5) | ((t & 1) << 4))) = v;
+                }
+            }
+            tmem_wait_st();
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            mbar_arrive(&sh.ds_ready);
+
+            // drain dQ of this query tile (lane = query row)
+            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, it & 1, W_DQFULL, it));
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int q = q0 + row;
+            float* dq_row = dq_bh + (int64_t)q * a.dq_sM;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                tmem_ld32(trow + COL_DQ + c * 32, rs);
+                tmem_wait_ld();
+                if (q < a.Tq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        red_add_v4(dq_row + c * 32 + i, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]),
+                                   __uint_as_float(rs[i + 2]), __uint_as_float(rs[i + 3]));
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&sh.dq_empty);
+        }
+
+        // epilogue: dV and dK of this KV tile (the last dq_full covered every MMA issued)
+        tc_fence_after_sync();
+        float* dv_row = a.dV + (int64_t)b * a.dv_sB + (int64_t)h * a.dv_sH + (int64_t)kvrow * a.dv_sM;
+        float* dk_row = a.dK + (int64_t)b * a.dk_sB + (int64_t)h * a.dk_sH + (int64_t)kvrow * a.dk_sM;
+#pragma unroll 1
+        for (int t = 0; t < 4; ++t) {
+            const int col = (t < 2) ? COL_DV + t * 32 : COL_DK + (t - 2) * 32;
+            float* dst = ((t < 2) ? dv_row : dk_row) + (t & 1) * 32;
+            if (ok && n_it > 0) {
+                tmem_ld32(trow + col, rs);
+                tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) rs[i] = 0u;
+            }
+            if (kv_ok) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    float4 v = make_float4(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1]), __uint_as_float(rs[i + 2]),
+                                           __uint_as_float(rs[i + 3]));
+                    float4* d4 = reinterpret_cast<float4*>(dst + i);
+                    if (a.accum_dkdv) {
+                        const float4 o = *d4;
+                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                    }
+                    *d4 = v;
+                }
+            }
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+int launch_attn_bwd(const BwdMaps& m, const BwdArgs& a, cudaStream_t stream) {
+    static bool attr_done[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return HK_ERR_CUDA;
+    if (dev < 64 && !attr_done[dev]) {
+        if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd::SMEM_BYTES) !=
+            cudaSuccess)
+            return HK_ERR_CUDA;
+        attr_done[dev] = true;
+    }
+    const long long nblocks = (long long)a.n_kvtiles * a.BH;
+    if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
+    attn_bwd_kernel<<<(unsigned)nblocks, bwd::NUM_THREADS, bwd::SMEM_BYTES, stream>>>(m.q, m.k, m.v, m.dO, m.q_mn, m.k_mn,
+                                                                                       m.dO_mn, a);
+    count_launch();
+    return check_launch();
+}
+
+}  // namespace hk

@@ -1,0 +1,59 @@
+// attn_kernels.cuh -- argument blocks and launchers of the two tensor-core kernels.
+#pragma once
+#include "attn_common.cuh"
+
+namespace hk {
+
+struct FwdArgs {
+    float* O;
+    float* LSE;
+    const float* mask;  // dense dropout mask [BH, Tq, Tk] or nullptr
+    int64_t o_sB, o_sM, o_sH, lse_sB, lse_sH;
+    int H, BH;
+    int Tq, Tk;
+    int n_qtiles;
+    int q_pos0, k_pos0;
+    float scale_log2e;
+    int causal;
+    int dropout_mode;  // 0 none, 1 dense mask, 2 Philox
+    uint32_t drop_thr;
+    uint64_t seed, offset;
+    DeviceStatus* status;
+};
+
+int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdArgs& a,
+                    cudaStream_t stream);
+
+struct BwdArgs {
+    const float* LSE;
+    const float* D;
+    float* dQ;
+    float* dK;
+    float* dV;
+    const float* mask;
+    int64_t lse_sB, lse_sH, d_sB, d_sH;
+    int64_t dq_sB, dq_sM, dq_sH, dk_sB, dk_sM, dk_sH, dv_sB, dv_sM, dv_sH;
+    int H, BH;
+    int Tq, Tk;
+    int n_kvtiles;
+    int q_pos0, k_pos0;
+    float scale, scale_log2e;
+    int causal;
+    int accum_dkdv;
+    int dropout_mode;
+    uint32_t drop_thr;
+    uint64_t seed, offset;
+    DeviceStatus* status;
+};
+
+// K-major maps (16-byte-chunk swizzle) of Q, K, V, dO and MN-major maps
+// (32-byte-chunk swizzle) of Q, K, dO over the same memory.
+struct BwdMaps {
+    CUtensorMap q, k, v, dO, q_mn, k_mn, dO_mn;
+};
+
+int launch_attn_bwd(const BwdMaps& m, const BwdArgs& a, cudaStream_t stream);
+
+int run_umma_selftest(int which, const float* A, const float* B, float* out, cudaStream_t stream);
+
+}  // namespace hk

@@ -1,0 +1,177 @@
+// attn_prepass.cu -- the HBM-bound helper kernels around the two tensor-core
+// kernels: TF32 operand rounding, D = rowsum(dO * O), dQ zeroing and the
+// softmax merge of two partial forward results.
+#include "attn_prepass.cuh"
+
+#include <algorithm>
+
+namespace hk {
+
+// ---------------------------------------------------------------------------
+// TF32 operand rounding.  The reference adds 0x1000 to the bit pattern of every
+// MMA operand as it loads it from shared memory
+// (fused_attn_forward_kernel_tc_sm89.cu:197,209-210,219;
+//  mem_efficient_bwd_unified_kernel_exp12.cu:118,127,136), i.e. round to
+// nearest, ties away.  tcgen05.mma reads its operands straight from the bytes
+// TMA wrote, so the rounding is applied once here, into contiguous
+// [BH, T, 64] copies in the caller's workspace.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) round_tf32_kernel(const RoundJob job) {
+    const int t = blockIdx.y;
+    const int T = job.T[t];
+    const int H = job.H;
+    const View4 v = job.src[t];
+    uint4* dst = reinterpret_cast<uint4*>(job.dst[t]);
+    const long long nvec = (long long)job.BH * T * 16;  // 16 float4 per 64-float row
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i >> 4;
+        const int c4 = (int)(i & 15);
+        const int bh = (int)(row / T);
+        const int r = (int)(row - (long long)bh * T);
+        const int b = bh / H, h = bh - b * H;
+        const float4 x =
+            __ldg(reinterpret_cast<const float4*>(v.ptr + (int64_t)b * v.sB + (int64_t)h * v.sH + (int64_t)r * v.sM) + c4);
+        uint4 y;
+        y.x = tf32_round_bits(__float_as_uint(x.x));
+        y.y = tf32_round_bits(__float_as_uint(x.y));
+        y.z = tf32_round_bits(__float_as_uint(x.z));
+        y.w = tf32_round_bits(__float_as_uint(x.w));
+        dst[i] = y;
+    }
+}
+
+int launch_round_tf32(const RoundJob& job, cudaStream_t stream) {
+    long long max_vec = 0;
+    for (int t = 0; t < job.n; ++t) max_vec = std::max(max_vec, (long long)job.BH * job.T[t] * 16);
+    if (max_vec == 0 || job.n == 0) return HK_OK;
+    const int blocks = (int)std::min<long long>((max_vec + 255) / 256, 148 * 8);
+    round_tf32_kernel<<<dim3(blocks, job.n), 256, 0, stream>>>(job);
+    count_launch();
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------
+// D[b,h,i] = sum_k dO[i,k] * O[i,k]  (mem_efficient_bwd_precompute_D_sm89.cu:45-91),
+// 16 lanes per row, one float4 of each operand per lane.  Optionally also
+// writes the TF32-rounded copy of dO the backward MMAs consume, so dO is read
+// from HBM once.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) precompute_D_kernel(const DJob j) {
+    const long long nrows = (long long)j.BH * j.T;
+    const int sub = threadIdx.x & 15;
+    for (long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4; row < ((nrows + 15) & ~15ll);
+         row += ((long long)gridDim.x * blockDim.x) >> 4) {
+        float s = 0.f;
+        if (row < nrows) {
+            const int bh = (int)(row / j.T);
+            const int r = (int)(row - (long long)bh * j.T);
+            const int b = bh / j.H, h = bh - b * j.H;
+            const float4 g = __ldg(
+                reinterpret_cast<const float4*>(j.dO.ptr + (int64_t)b * j.dO.sB + (int64_t)h * j.dO.sH + (int64_t)r * j.dO.sM) +
+                sub);
+            const float4 o = __ldg(
+                reinterpret_cast<const float4*>(j.O.ptr + (int64_t)b * j.O.sB + (int64_t)h * j.O.sH + (int64_t)r * j.O.sM) + sub);
+            s = g.x * o.x + g.y * o.y + g.z * o.z + g.w * o.w;
+            if (j.dO_rounded) {
+                uint4 y;
+                y.x = tf32_round_bits(__float_as_uint(g.x));
+                y.y = tf32_round_bits(__float_as_uint(g.y));
+                y.z = tf32_round_bits(__float_as_uint(g.z));
+                y.w = tf32_round_bits(__float_as_uint(g.w));
+                reinterpret_cast<uint4*>(j.dO_rounded)[row * 16 + sub] = y;
+            }
+        }
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (row < nrows && sub == 0) {
+            const int bh = (int)(row / j.T);
+            const int r = (int)(row - (long long)bh * j.T);
+            const int b = bh / j.H, h = bh - b * j.H;
+            j.D[(int64_t)b * j.d_sB + (int64_t)h * j.d_sH + r] = s;
+        }
+    }
+}
+
+int launch_precompute_D(const DJob& j, cudaStream_t stream) {
+    const long long nrows = (long long)j.BH * j.T;
+    if (nrows == 0) return HK_OK;
+    const int blocks = (int)std::min<long long>((nrows * 16 + 255) / 256, 148 * 8);
+    precompute_D_kernel<<<blocks, 256, 0, stream>>>(j);
+    count_launch();
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------
+// zero a strided [B, H, T, 64] tensor (dQ is accumulated with atomics; the
+// reference leaves this to its caller, kernels_test.cu:562)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) zero_rows_kernel(float* ptr, int64_t sB, int64_t sM, int64_t sH, int H, int T,
+                                                        long long nvec) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i >> 4;
+        const int c4 = (int)(i & 15);
+        const int bh = (int)(row / T);
+        const int r = (int)(row - (long long)bh * T);
+        const int b = bh / H, h = bh - b * H;
+        reinterpret_cast<float4*>(ptr + (int64_t)b * sB + (int64_t)h * sH + (int64_t)r * sM)[c4] =
+            make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+int launch_zero_rows(float* ptr, int64_t sB, int64_t sM, int64_t sH, int B, int H, int T, cudaStream_t stream) {
+    const long long nvec = (long long)B * H * T * 16;
+    if (nvec == 0) return HK_OK;
+    const int blocks = (int)std::min<long long>((nvec + 255) / 256, 148 * 8);
+    zero_rows_kernel<<<blocks, 256, 0, stream>>>(ptr, sB, sM, sH, H, T, nvec);
+    count_launch();
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------
+// (O_acc, LSE_acc) <- merge with (O_part, LSE_part): both are normalised
+// softmax outputs over disjoint key sets, so
+//   LSE = log(exp(LSE_a) + exp(LSE_p)),  O = O_a * exp(LSE_a - LSE) + O_p * exp(LSE_p - LSE).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) merge_partial_kernel(float* O_acc, float* LSE_acc, const float* O_part,
+                                                            const float* LSE_part, long long rows) {
+    const int sub = threadIdx.x & 15;
+    // both half-warps of a warp run the same number of iterations (bound rounded up to even)
+    for (long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4; row < ((rows + 1) & ~1ll);
+         row += ((long long)gridDim.x * blockDim.x) >> 4) {
+        const bool valid = row < rows;
+        float wa = 0.f, wp = 0.f, lse = -INFINITY;
+        if (valid) {
+            const float la = LSE_acc[row], lp = LSE_part[row];
+            const float mx = fmaxf(la, lp);
+            if (mx > -INFINITY) {
+                const float ea = expf(la - mx), ep = expf(lp - mx);
+                const float inv = 1.f / (ea + ep);
+                wa = ea * inv;
+                wp = ep * inv;
+                lse = mx + logf(ea + ep);
+            }
+            float4 x = reinterpret_cast<float4*>(O_acc)[row * 16 + sub];
+            const float4 y = __ldg(reinterpret_cast<const float4*>(O_part) + row * 16 + sub);
+            x.x = x.x * wa + y.x * wp;
+            x.y = x.y * wa + y.y * wp;
+            x.z = x.z * wa + y.z * wp;
+            x.w = x.w * wa + y.w * wp;
+            reinterpret_cast<float4*>(O_acc)[row * 16 + sub] = x;
+        }
+        __syncwarp();  // every lane has read LSE_acc[row] before lane 0 overwrites it
+        if (valid && sub == 0) LSE_acc[row] = lse;
+    }
+}
+
+int launch_merge_partial(float* O_acc, float* LSE_acc, const float* O_part, const float* LSE_part, long long rows,
+                         cudaStream_t stream) {
+    if (rows == 0) return HK_OK;
+    const int blocks = (int)std::min<long long>((rows * 16 + 255) / 256, 148 * 8);
+    merge_partial_kernel<<<blocks, 256, 0, stream>>>(O_acc, LSE_acc, O_part, LSE_part, rows);
+    count_launch();
+    return check_launch();
+}
+
+}  // namespace hk

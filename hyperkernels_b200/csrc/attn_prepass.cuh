@@ -1,0 +1,30 @@
+// attn_prepass.cuh -- launchers of the HBM-bound helper kernels (attn_prepass.cu).
+#pragma once
+#include "attn_common.cuh"
+
+namespace hk {
+
+struct RoundJob {
+    View4 src[4];
+    float* dst[4];  // contiguous [BH, T[t], 64]
+    int T[4];
+    int H, BH;
+    int n;
+};
+int launch_round_tf32(const RoundJob& job, cudaStream_t stream);
+
+struct DJob {
+    View4 dO, O;
+    float* D;
+    int64_t d_sB, d_sH;
+    float* dO_rounded;  // contiguous [BH, T, 64] or nullptr
+    int H, BH, T;
+};
+int launch_precompute_D(const DJob& j, cudaStream_t stream);
+
+int launch_zero_rows(float* ptr, int64_t sB, int64_t sM, int64_t sH, int B, int H, int T, cudaStream_t stream);
+
+int launch_merge_partial(float* O_acc, float* LSE_acc, const float* O_part, const float* LSE_part, long long rows,
+                         cudaStream_t stream);
+
+}  // namespace hk

@@ -1,0 +1,372 @@
+// hk_api.cu -- the extern "C" boundary declared in include/hk_attention.h:
+// argument validation, workspace carving, tensor-map construction and the
+// launch sequence of each entry point.  No device memory is allocated here.
+#include <atomic>
+#include <cmath>
+#include <cstddef>
+#include <cstring>
+#include <mutex>
+
+#include "attn_kernels.cuh"
+#include "attn_prepass.cuh"
+#include "philox.h"
+
+// The leading bytes of both argument blocks must be the reference's by-value
+// structs (fused_attn_forward_kernel_tc_sm89.cu:8-29, 192 bytes;
+// mem_efficient_bwd_unified_kernel_exp12.cu:11-38, 328 bytes).
+static_assert(offsetof(hk_attn_fwd_params, Q) == 0 && offsetof(hk_attn_fwd_params, LSE) == 32, "fwd head");
+static_assert(offsetof(hk_attn_fwd_params, B) == 40 && offsetof(hk_attn_fwd_params, nh) == 44, "fwd head");
+static_assert(offsetof(hk_attn_fwd_params, T) == 48 && offsetof(hk_attn_fwd_params, scale) == 56, "fwd head");
+static_assert(offsetof(hk_attn_fwd_params, is_causal) == 60 && offsetof(hk_attn_fwd_params, dropout_p) == 64, "fwd head");
+static_assert(offsetof(hk_attn_fwd_params, dropout_mask) == 72 && offsetof(hk_attn_fwd_params, q_strideB) == 80, "fwd head");
+static_assert(offsetof(hk_attn_fwd_params, lse_strideH) == 184 && offsetof(hk_attn_fwd_params, dropout_seed) == 192, "fwd head");
+static_assert(offsetof(hk_attn_bwd_params, D) == 48 && offsetof(hk_attn_bwd_params, dV) == 72, "bwd head");
+static_assert(offsetof(hk_attn_bwd_params, B) == 80 && offsetof(hk_attn_bwd_params, T) == 88, "bwd head");
+static_assert(offsetof(hk_attn_bwd_params, scale) == 92 && offsetof(hk_attn_bwd_params, is_causal) == 96, "bwd head");
+static_assert(offsetof(hk_attn_bwd_params, q_strideB) == 104 && offsetof(hk_attn_bwd_params, d_strideH) == 320, "bwd head");
+static_assert(sizeof(hk_attn_fwd_params) == 256 && sizeof(hk_attn_bwd_params) == 400, "block sizes");
+static_assert(offsetof(hk_attn_bwd_params, dropout_p) == 328, "bwd tail starts after the 328-byte reference block");
+
+namespace hk {
+
+
+// ---- process-wide state ------------------------------------------------------
+static std::atomic<uint64_t> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+int check_launch() { return cudaGetLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA; }
+
+__device__ DeviceStatus g_device_status;  // one instance per device that loads the module
+
+DeviceStatus* device_status_ptr() {
+    static DeviceStatus* cache[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cache[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+        cache[dev] = static_cast<DeviceStatus*>(p);
+    }
+    return cache[dev];
+}
+
+EncodeTiledFn get_encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+int make_tile_map(CUtensorMap* map, const float* ptr, int inner, int B, int H, int64_t T, int64_t sB, int64_t sM,
+                  int64_t sH, int box_rows, bool mn_major) {
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return HK_ERR_CUDA;
+    // A size-1 dimension may carry any stride; give it a harmless valid one.
+    if (H == 1) sH = sM * T;
+    if (B == 1) sB = (sH * H > sM * T) ? sH * H : sM * T;
+    cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)sM * 4, (cuuint64_t)sH * 4, (cuuint64_t)sB * 4};
+    cuuint32_t box[4] = {(cuuint32_t)HALF_D, (cuuint32_t)box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? HK_OK : HK_ERR_CUDA;
+}
+
+// ---- validation helpers -------------------------------------------------------
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline bool stride_ok(int64_t s) { return s >= 0 && (s % 4) == 0; }
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace hk
+
+using namespace hk;
+
+extern "C" {
+
+const char* hk_status_string(int s) {
+    switch (s) {
+        case HK_OK: return "ok";
+        case HK_ERR_NULL_POINTER: return "null pointer";
+        case HK_ERR_BAD_SHAPE: return "bad shape";
+        case HK_ERR_MISALIGNED: return "pointer or stride not 16-byte aligned";
+        case HK_ERR_BAD_DROPOUT: return "bad dropout arguments";
+        case HK_ERR_WORKSPACE: return "workspace missing or too small";
+        case HK_ERR_UNSUPPORTED: return "unsupported combination";
+        case HK_ERR_CUDA: return "CUDA error";
+        case HK_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
+        default: return "unknown status";
+    }
+}
+
+uint64_t hk_attn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int hk_attn_last_device_status(void) {
+    DeviceStatus* d = device_status_ptr();
+    if (!d) return HK_ERR_CUDA;
+    if (cudaDeviceSynchronize() != cudaSuccess) return HK_ERR_CUDA;
+    DeviceStatus h;
+    if (cudaMemcpy(&h, d, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return HK_ERR_CUDA;
+    if (h.code != 0) {
+        DeviceStatus z = {0, 0, 0, 0};
+        cudaMemcpy(d, &z, sizeof(z), cudaMemcpyHostToDevice);
+        return HK_ERR_DEVICE_TIMEOUT;
+    }
+    return HK_OK;
+}
+
+int hk_attn_dropout_mask(float* mask, int BH, int64_t Tq, int64_t Tk, float p, uint64_t seed, uint64_t offset,
+                         int64_t q_pos0, int64_t k_pos0) {
+    if (!mask) return HK_ERR_NULL_POINTER;
+    if (!(p >= 0.f && p < 1.f)) return HK_ERR_BAD_DROPOUT;
+    if (BH < 0 || Tq < 0 || Tk < 0) return HK_ERR_BAD_SHAPE;
+    const uint32_t thr = hk_philox_threshold(p);
+    for (int bh = 0; bh < BH; ++bh)
+        for (int64_t i = 0; i < Tq; ++i) {
+            float* row = mask + ((size_t)bh * Tq + i) * Tk;
+            for (int64_t j = 0; j < Tk; ++j)
+                row[j] = hk_philox_keep(seed, offset, (uint32_t)bh, (uint32_t)(q_pos0 + i), (uint32_t)(k_pos0 + j), thr)
+                             ? 1.0f
+                             : 0.0f;
+        }
+    return HK_OK;
+}
+
+size_t hk_attn_fwd_workspace_bytes(const hk_attn_fwd_params* p) {
+    if (!p || (p->flags & HK_FLAG_OPERANDS_PREROUNDED)) return 0;
+    if (p->B <= 0 || p->nh <= 0 || p->T <= 0) return 0;
+    const int64_t Tk = p->kv_len > 0 ? p->kv_len : p->T;
+    const size_t bh = (size_t)p->B * p->nh;
+    return align_up(bh * p->T * 256, 256) + 2 * align_up(bh * Tk * 256, 256);
+}
+
+size_t hk_attn_bwd_workspace_bytes(const hk_attn_bwd_params* p) {
+    if (!p || (p->flags & HK_FLAG_OPERANDS_PREROUNDED)) return 0;
+    if (p->B <= 0 || p->nh <= 0 || p->T <= 0) return 0;
+    const int64_t Tk = p->kv_len > 0 ? p->kv_len : p->T;
+    const size_t bh = (size_t)p->B * p->nh;
+    return 2 * align_up(bh * p->T * 256, 256) + 2 * align_up(bh * Tk * 256, 256);  // Q, dO, K, V
+}
+
+static int validate_dropout(float p, const float* mask, uint32_t flags, int64_t k_pos0, int* mode) {
+    *mode = 0;
+    if (!(p >= 0.f && p < 1.f)) return HK_ERR_BAD_DROPOUT;
+    const bool philox = (flags & HK_FLAG_PHILOX_DROPOUT) != 0;
+    if (philox && mask) return HK_ERR_BAD_DROPOUT;
+    if (p > 0.f) {
+        if (philox) {
+            if (k_pos0 % 4 != 0) return HK_ERR_UNSUPPORTED;
+            *mode = 2;
+        } else if (mask) {
+            *mode = 1;  // reference semantics: active only when p > 0 and mask != nullptr
+        }
+    }
+    return HK_OK;
+}
+
+int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!p) return HK_ERR_NULL_POINTER;
+    if (!p->Q || !p->K || !p->V || !p->O || !p->LSE) return HK_ERR_NULL_POINTER;
+    const int64_t Tq = p->T, Tk = p->kv_len > 0 ? p->kv_len : p->T;
+    if (p->B <= 0 || p->nh <= 0 || Tq <= 0 || p->kv_len < 0) return HK_ERR_BAD_SHAPE;
+    if (Tq > (1 << 30) || Tk > (1 << 30) || (int64_t)p->B * p->nh > (1 << 24)) return HK_ERR_BAD_SHAPE;
+    if (p->q_pos0 < 0 || p->k_pos0 < 0 || p->q_pos0 + Tq > (1LL << 31) - 1 || p->k_pos0 + Tk > (1LL << 31) - 1)
+        return HK_ERR_BAD_SHAPE;
+    if (!aligned16(p->Q) || !aligned16(p->K) || !aligned16(p->V) || !aligned16(p->O)) return HK_ERR_MISALIGNED;
+    const int64_t st[] = {p->q_strideB, p->q_strideM, p->q_strideH, p->k_strideB, p->k_strideM, p->k_strideH,
+                          p->v_strideB, p->v_strideM, p->v_strideH, p->o_strideB, p->o_strideM, p->o_strideH};
+    for (int64_t s : st)
+        if (!stride_ok(s)) return HK_ERR_MISALIGNED;
+    if (p->q_strideM < HEAD_DIM || p->k_strideM < HEAD_DIM || p->v_strideM < HEAD_DIM || p->o_strideM < HEAD_DIM)
+        return HK_ERR_BAD_SHAPE;
+    if (!std::isfinite(p->scale)) return HK_ERR_BAD_SHAPE;
+    int mode = 0;
+    int rc = validate_dropout(p->dropout_p, p->dropout_mask, p->flags, p->k_pos0, &mode);
+    if (rc != HK_OK) return rc;
+
+    const int B = p->B, H = p->nh, BH = B * H;
+    CUtensorMap mq, mk, mv;
+    if (p->flags & HK_FLAG_OPERANDS_PREROUNDED) {
+        if ((rc = make_tile_map(&mq, p->Q, HEAD_DIM, B, H, Tq, p->q_strideB, p->q_strideM, p->q_strideH, TILE))) return rc;
+        if ((rc = make_tile_map(&mk, p->K, HEAD_DIM, B, H, Tk, p->k_strideB, p->k_strideM, p->k_strideH, TILE))) return rc;
+        if ((rc = make_tile_map(&mv, p->V, HEAD_DIM, B, H, Tk, p->v_strideB, p->v_strideM, p->v_strideH, TILE, true))) return rc;
+    } else {
+        const size_t need = hk_attn_fwd_workspace_bytes(p);
+        if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u))
+            return HK_ERR_WORKSPACE;
+        uint8_t* ws = static_cast<uint8_t*>(p->workspace);
+        float* qr = reinterpret_cast<float*>(ws);
+        float* kr = reinterpret_cast<float*>(ws + align_up((size_t)BH * Tq * 256, 256));
+        float* vr = reinterpret_cast<float*>(ws + align_up((size_t)BH * Tq * 256, 256) + align_up((size_t)BH * Tk * 256, 256));
+        RoundJob job{};
+        job.src[0] = View4{p->Q, p->q_strideB, p->q_strideM, p->q_strideH};
+        job.src[1] = View4{p->K, p->k_strideB, p->k_strideM, p->k_strideH};
+        job.src[2] = View4{p->V, p->v_strideB, p->v_strideM, p->v_strideH};
+        job.dst[0] = qr; job.dst[1] = kr; job.dst[2] = vr;
+        job.T[0] = (int)Tq; job.T[1] = (int)Tk; job.T[2] = (int)Tk;
+        job.H = H; job.BH = BH; job.n = 3;
+        if ((rc = launch_round_tf32(job, stream))) return rc;
+        if ((rc = make_tile_map(&mq, qr, HEAD_DIM, B, H, Tq, (int64_t)H * Tq * 64, 64, Tq * 64, TILE))) return rc;
+        if ((rc = make_tile_map(&mk, kr, HEAD_DIM, B, H, Tk, (int64_t)H * Tk * 64, 64, Tk * 64, TILE))) return rc;
+        if ((rc = make_tile_map(&mv, vr, HEAD_DIM, B, H, Tk, (int64_t)H * Tk * 64, 64, Tk * 64, TILE, true))) return rc;
+    }
+
+    FwdArgs a{};
+    a.O = p->O; a.LSE = p->LSE;
+    a.mask = (mode == 1) ? p->dropout_mask : nullptr;
+    a.o_sB = p->o_strideB; a.o_sM = p->o_strideM; a.o_sH = p->o_strideH;
+    a.lse_sB = p->lse_strideB; a.lse_sH = p->lse_strideH;
+    a.H = H; a.BH = BH; a.Tq = (int)Tq; a.Tk = (int)Tk;
+    a.n_qtiles = (int)((Tq + TILE - 1) / TILE);
+    a.q_pos0 = (int)p->q_pos0; a.k_pos0 = (int)p->k_pos0;
+    a.scale_log2e = p->scale * LOG2E;
+    a.causal = p->is_causal ? 1 : 0;
+    a.dropout_mode = mode;
+    a.drop_thr = hk_philox_threshold(p->dropout_p);
+    a.seed = p->dropout_seed; a.offset = p->dropout_offset;
+    a.status = device_status_ptr();
+    if (!a.status) return HK_ERR_CUDA;
+    return launch_attn_fwd(mq, mk, mv, a, stream);
+}
+
+int hk_attn_bwd_precompute_D(const hk_attn_bwd_params* p, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!p) return HK_ERR_NULL_POINTER;
+    if (!p->dO || !p->O || !p->D) return HK_ERR_NULL_POINTER;
+    if (p->B <= 0 || p->nh <= 0 || p->T <= 0) return HK_ERR_BAD_SHAPE;
+    if (!aligned16(p->dO) || !aligned16(p->O)) return HK_ERR_MISALIGNED;
+    const int64_t st[] = {p->o_strideB, p->o_strideM, p->o_strideH, p->do_strideB, p->do_strideM, p->do_strideH};
+    for (int64_t s : st)
+        if (!stride_ok(s)) return HK_ERR_MISALIGNED;
+    DJob j{};
+    j.dO = View4{p->dO, p->do_strideB, p->do_strideM, p->do_strideH};
+    j.O = View4{p->O, p->o_strideB, p->o_strideM, p->o_strideH};
+    j.D = p->D; j.d_sB = p->d_strideB; j.d_sH = p->d_strideH;
+    j.dO_rounded = nullptr;
+    j.H = p->nh; j.BH = p->B * p->nh; j.T = p->T;
+    return launch_precompute_D(j, stream);
+}
+
+int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!p) return HK_ERR_NULL_POINTER;
+    if (!p->Q || !p->K || !p->V || !p->dO || !p->LSE || !p->D || !p->dQ || !p->dK || !p->dV) return HK_ERR_NULL_POINTER;
+    const bool d_given = (p->flags & HK_FLAG_D_PRECOMPUTED) != 0;
+    if (!d_given && !p->O) return HK_ERR_NULL_POINTER;
+    const int64_t Tq = p->T, Tk = p->kv_len > 0 ? p->kv_len : p->T;
+    if (p->B <= 0 || p->nh <= 0 || Tq <= 0 || p->kv_len < 0) return HK_ERR_BAD_SHAPE;
+    if (Tk > (1 << 30) || (int64_t)p->B * p->nh > (1 << 24)) return HK_ERR_BAD_SHAPE;
+    if (p->q_pos0 < 0 || p->k_pos0 < 0 || p->q_pos0 + Tq > (1LL << 31) - 1 || p->k_pos0 + Tk > (1LL << 31) - 1)
+        return HK_ERR_BAD_SHAPE;
+    const void* ptrs[] = {p->Q, p->K, p->V, p->dO, p->dQ, p->dK, p->dV};
+    for (const void* q : ptrs)
+        if (!aligned16(q)) return HK_ERR_MISALIGNED;
+    if (!d_given && !aligned16(p->O)) return HK_ERR_MISALIGNED;
+    const int64_t st[] = {p->q_strideB,  p->q_strideM,  p->q_strideH,  p->k_strideB,  p->k_strideM,  p->k_strideH,
+                          p->v_strideB,  p->v_strideM,  p->v_strideH,  p->o_strideB,  p->o_strideM,  p->o_strideH,
+                          p->do_strideB, p->do_strideM, p->do_strideH, p->dq_strideB, p->dq_strideM, p->dq_strideH,
+                          p->dk_strideB, p->dk_strideM, p->dk_strideH, p->dv_strideB, p->dv_strideM, p->dv_strideH};
+    for (int64_t s : st)
+        if (!stride_ok(s)) return HK_ERR_MISALIGNED;
+    if (p->q_strideM < HEAD_DIM || p->k_strideM < HEAD_DIM || p->v_strideM < HEAD_DIM || p->do_strideM < HEAD_DIM ||
+        p->dq_strideM < HEAD_DIM || p->dk_strideM < HEAD_DIM || p->dv_strideM < HEAD_DIM)
+        return HK_ERR_BAD_SHAPE;
+    if (!std::isfinite(p->scale)) return HK_ERR_BAD_SHAPE;
+    int mode = 0;
+    int rc = validate_dropout(p->dropout_p, p->dropout_mask, p->flags, p->k_pos0, &mode);
+    if (rc != HK_OK) return rc;
+
+    const int B = p->B, H = p->nh, BH = B * H;
+    const View4 vQ{p->Q, p->q_strideB, p->q_strideM, p->q_strideH}, vK{p->K, p->k_strideB, p->k_strideM, p->k_strideH},
+        vV{p->V, p->v_strideB, p->v_strideM, p->v_strideH}, vdO{p->dO, p->do_strideB, p->do_strideM, p->do_strideH},
+        vO{p->O, p->o_strideB, p->o_strideM, p->o_strideH};
+    BwdMaps m;
+    float* dO_rounded = nullptr;
+    // the tensors the MMAs read: the caller's (pre-rounded) or the rounded copies in the workspace
+    View4 tQ = vQ, tK = vK, tV = vV, tdO = vdO;
+    if (!(p->flags & HK_FLAG_OPERANDS_PREROUNDED)) {
+        const size_t need = hk_attn_bwd_workspace_bytes(p);
+        if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u))
+            return HK_ERR_WORKSPACE;
+        uint8_t* ws = static_cast<uint8_t*>(p->workspace);
+        const size_t qb = align_up((size_t)BH * Tq * 256, 256), kb = align_up((size_t)BH * Tk * 256, 256);
+        float* qr = reinterpret_cast<float*>(ws);
+        dO_rounded = reinterpret_cast<float*>(ws + qb);
+        float* kr = reinterpret_cast<float*>(ws + 2 * qb);
+        float* vr = reinterpret_cast<float*>(ws + 2 * qb + kb);
+        RoundJob job{};
+        job.src[0] = vQ; job.src[1] = vK; job.src[2] = vV; job.src[3] = vdO;
+        job.dst[0] = qr; job.dst[1] = kr; job.dst[2] = vr; job.dst[3] = dO_rounded;
+        job.T[0] = (int)Tq; job.T[1] = (int)Tk; job.T[2] = (int)Tk; job.T[3] = (int)Tq;
+        job.H = H; job.BH = BH;
+        job.n = d_given ? 4 : 3;  // otherwise the D pre-pass writes the rounded dO while it reads dO
+        if ((rc = launch_round_tf32(job, stream))) return rc;
+        tQ = View4{qr, (int64_t)H * Tq * 64, 64, Tq * 64};
+        tdO = View4{dO_rounded, (int64_t)H * Tq * 64, 64, Tq * 64};
+        tK = View4{kr, (int64_t)H * Tk * 64, 64, Tk * 64};
+        tV = View4{vr, (int64_t)H * Tk * 64, 64, Tk * 64};
+    }
+    if ((rc = make_tile_map(&m.q, tQ.ptr, HEAD_DIM, B, H, Tq, tQ.sB, tQ.sM, tQ.sH, TILE, false))) return rc;
+    if ((rc = make_tile_map(&m.k, tK.ptr, HEAD_DIM, B, H, Tk, tK.sB, tK.sM, tK.sH, TILE, false))) return rc;
+    if ((rc = make_tile_map(&m.v, tV.ptr, HEAD_DIM, B, H, Tk, tV.sB, tV.sM, tV.sH, TILE, false))) return rc;
+    if ((rc = make_tile_map(&m.dO, tdO.ptr, HEAD_DIM, B, H, Tq, tdO.sB, tdO.sM, tdO.sH, TILE, false))) return rc;
+    if ((rc = make_tile_map(&m.q_mn, tQ.ptr, HEAD_DIM, B, H, Tq, tQ.sB, tQ.sM, tQ.sH, TILE, true))) return rc;
+    if ((rc = make_tile_map(&m.k_mn, tK.ptr, HEAD_DIM, B, H, Tk, tK.sB, tK.sM, tK.sH, TILE, true))) return rc;
+    if ((rc = make_tile_map(&m.dO_mn, tdO.ptr, HEAD_DIM, B, H, Tq, tdO.sB, tdO.sM, tdO.sH, TILE, true))) return rc;
+    if (!d_given) {
+        DJob j{};
+        j.dO = vdO; j.O = vO;
+        j.D = p->D; j.d_sB = p->d_strideB; j.d_sH = p->d_strideH;
+        j.dO_rounded = dO_rounded;
+        j.H = H; j.BH = BH; j.T = (int)Tq;
+        if ((rc = launch_precompute_D(j, stream))) return rc;
+    }
+    if (!(p->flags & HK_FLAG_ACCUM_DQ))
+        if ((rc = launch_zero_rows(p->dQ, p->dq_strideB, p->dq_strideM, p->dq_strideH, B, H, (int)Tq, stream))) return rc;
+
+    BwdArgs a{};
+    a.LSE = p->LSE; a.D = p->D; a.dQ = p->dQ; a.dK = p->dK; a.dV = p->dV;
+    a.mask = (mode == 1) ? p->dropout_mask : nullptr;
+    a.lse_sB = p->lse_strideB; a.lse_sH = p->lse_strideH; a.d_sB = p->d_strideB; a.d_sH = p->d_strideH;
+    a.dq_sB = p->dq_strideB; a.dq_sM = p->dq_strideM; a.dq_sH = p->dq_strideH;
+    a.dk_sB = p->dk_strideB; a.dk_sM = p->dk_strideM; a.dk_sH = p->dk_strideH;
+    a.dv_sB = p->dv_strideB; a.dv_sM = p->dv_strideM; a.dv_sH = p->dv_strideH;
+    a.H = H; a.BH = BH; a.Tq = (int)Tq; a.Tk = (int)Tk;
+    a.n_kvtiles = (int)((Tk + TILE - 1) / TILE);
+    a.q_pos0 = (int)p->q_pos0; a.k_pos0 = (int)p->k_pos0;
+    a.scale = p->scale; a.scale_log2e = p->scale * LOG2E;
+    a.causal = p->is_causal ? 1 : 0;
+    a.accum_dkdv = (p->flags & HK_FLAG_ACCUM_DKDV) ? 1 : 0;
+    a.dropout_mode = mode;
+    a.drop_thr = hk_philox_threshold(p->dropout_p);
+    a.seed = p->dropout_seed; a.offset = p->dropout_offset;
+    a.status = device_status_ptr();
+    if (!a.status) return HK_ERR_CUDA;
+    return launch_attn_bwd(m, a, stream);
+}
+
+int hk_attn_merge_partial(float* O_acc, float* LSE_acc, const float* O_part, const float* LSE_part, int64_t rows,
+                          void* stream_) {
+    if (!O_acc || !LSE_acc || !O_part || !LSE_part) return HK_ERR_NULL_POINTER;
+    if (rows < 0) return HK_ERR_BAD_SHAPE;
+    if (!aligned16(O_acc) || !aligned16(O_part)) return HK_ERR_MISALIGNED;
+    return launch_merge_partial(O_acc, LSE_acc, O_part, LSE_part, rows, static_cast<cudaStream_t>(stream_));
+}
+
+int hk_attn_selftest(int which, const float* A, const float* B, float* out, void* stream_) {
+    return run_umma_selftest(which, A, B, out, static_cast<cudaStream_t>(stream_));
+}
+
+}  // extern "C"
