@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark driver: fused attention forward + backward (fp32 I/O, TF32 tensor cores).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C] [--impl ours|reference]
+
+A "step" is one forward + one backward over one batch of the chosen BASELINE
+config (default config 2, the GPT-2-small shape B=8, H=12, N=1024, d=64, causal,
+p=0).  With N GPUs every rank runs its own batch of that shape (the work is
+partitioned by batch x head, which needs no collective): weak scaling, value =
+total algorithmic FLOP/s over all ranks, time = max over ranks.
+
+FLOP convention (the reference's, README.md:148-151 of BlubridgeAI/HyperKernels):
+forward 4*B*H*N^2*d, backward 10*B*H*N^2*d, causal counts half.
+
+Printed line (rank 0): metric/value as above with inputs resident in HBM;
+`e2e` = the same metric through the C ABI with HOST (pinned) inputs and outputs,
+host<->device copies inside the timed region; `roofline` for the dominant kernel
+(the backward), timed with CUDA events around the kernel launches inside the
+timed region; `cpu_baseline` = the reference's own fp32 host attention timed on
+this box's cores (N = 1 only).
+"""
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    1: dict(B=2, H=4, N=256, causal=True, p=0.0, sigma=1.0, name="cfg1 B2 H4 N256 d64 causal p0"),
+    2: dict(B=8, H=12, N=1024, causal=True, p=0.0, sigma=1.0, name="cfg2 GPT-2-small B8 H12 N1024 d64 causal p0"),
+    3: dict(B=16, H=16, N=2048, causal=False, p=0.1, sigma=0.5, name="cfg3 B16 H16 N2048 d64 non-causal p0.1"),
+    4: dict(B=32, H=25, N=1024, causal=True, p=0.1, sigma=1.0, name="cfg4 GPT-2-XL B32 H25 N1024 d64 causal p0.1"),
+    5: dict(B=1, H=32, N=32768, causal=True, p=0.0, sigma=1.0, name="cfg5 B1 H32 N32768 d64 causal p0 (every 64th key x8)"),
+}
+METRIC = "attn fwd+bwd TF32 TFLOP/s"
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the backward kernel at the bench
+# workload (see profiles/); None until a capture exists for that config.
+NCU_TRAFFIC_BYTES = {}
+
+
+def flops(cfg, heads=None, fwd=True, bwd=True):
+    heads = cfg["B"] * cfg["H"] if heads is None else heads
+    f = (4.0 if fwd else 0.0) + (10.0 if bwd else 0.0)
+    return f * heads * cfg["N"] ** 2 * 64 * (0.5 if cfg["causal"] else 1.0)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        # dense TF32 runs at half the dense bf16 rate on the same tensor cores
+        return dict(tf32_tflops=p["bf16_tflops"] / 2.0, hbm_gbs=p["hbm_gbs"], source="measured (bf16 burst / 2)")
+    return dict(tf32_tflops=1590.0 / 2.0, hbm_gbs=6650.0, source="fallback (1.59 PF bf16 / 2)")
+
+
+# ---------------------------------------------------------------------------
+# reference CPU arm / cpu_baseline
+# ---------------------------------------------------------------------------
+def _cpu_lib():
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+
+    if ol.reference() is not None:
+        return ol, "reference"
+    return ol, "port"
+
+
+def _cpu_head(ol, kind, cfg, seed):
+    """One (b,h) slice, forward + backward, on one thread."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    N = cfg["N"]
+    Q, K, V, dO = ((rng.standard_normal((1, 1, N, 64)) * s).astype(np.float32)
+                   for s in (cfg["sigma"], cfg["sigma"], cfg["sigma"], 1.0))
+    t0 = time.perf_counter()
+    if kind == "reference":
+        O, L = ol.ref_attn_forward(Q, K, V, 0.125, int(cfg["causal"]))
+        ol.ref_attn_backward(Q, K, V, O, dO, L, 0.125, int(cfg["causal"]))
+    else:
+        O, L = ol.attn_forward(Q, K, V, 0.125, int(cfg["causal"]))
+        ol.attn_backward(Q, K, V, O, dO, L, 0.125, int(cfg["causal"]))
+    return time.perf_counter() - t0
+
+
+def cpu_batch(ol, kind, cfg, heads, cores, seed0=0):
+    """`heads` independent (b,h) slices over `cores` threads; returns wall seconds."""
+    import concurrent.futures as cf
+
+    t0 = time.perf_counter()
+    with cf.ThreadPoolExecutor(max_workers=cores) as ex:
+        list(ex.map(lambda i: _cpu_head(ol, kind, cfg, seed0 + i), range(heads)))
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(cfg, budget_core_s=12.0):
+    ol, kind = _cpu_lib()
+    cores = os.cpu_count() or 1
+    BH = cfg["B"] * cfg["H"]
+    heads_done, wall = 0, 0.0
+    while heads_done < BH and wall * cores < budget_core_s:
+        n = min(cores, BH - heads_done)
+        wall += cpu_batch(ol, kind, cfg, n, cores, seed0=heads_done)
+        heads_done += n
+    return dict(value=flops(cfg, heads_done) / wall / 1e12, unit="TFLOP/s", cores=cores, kind=kind,
+                sample=f"{heads_done} of {BH} (b,h) slices of {cfg['name']}, fwd+bwd, one slice per thread, "
+                       f"{wall:.2f} s wall" + ("" if heads_done == BH else " (bounded sample; slices are independent and equal-cost)"))
+
+
+def run_reference(args, cfg, rank, world):
+    if rank != 0:
+        return
+    ol, kind = _cpu_lib()
+    cores = os.cpu_count() or 1
+    BH = cfg["B"] * cfg["H"]
+    heads = min(cores, BH)
+    # keep a step near a second of wall time on long sequences
+    for _ in range(args.warmup):
+        cpu_batch(ol, kind, cfg, heads, cores)
+    t = [cpu_batch(ol, kind, cfg, heads, cores, seed0=17 * i) for i in range(args.steps)]
+    wall = sum(t)
+    value = flops(cfg, heads) * args.steps / wall / 1e12
+    sample = f"each step = {heads} of {BH} (b,h) slices of {cfg['name']}, fwd+bwd, one slice per thread"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (f64 accumulate)", "data": "synthetic",
+        "config": {"workload": cfg["name"], "config_id": args.config},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and clock-event reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            self.nv, self.h = nv, nv.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.001)
+
+    def start(self):
+        if self.nv is not None:
+            self._t = threading.Thread(target=self._loop, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t is not None:
+            self._t.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def run_ours(args, cfg, rank, local_rank, world):
+    import ctypes as C
+
+    import torch
+
+    import hyperkernels_b200 as hk
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the attention kernels have no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+
+        dist = dist_
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = hk.lib()
+    B, H, N, causal, p = cfg["B"], cfg["H"], cfg["N"], cfg["causal"], cfg["p"]
+    g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    shape = (B, H, N, 64)
+    Q, K, V = (torch.randn(shape, generator=g, device="cuda") * cfg["sigma"] for _ in range(3))
+    dO = torch.randn(shape, generator=g, device="cuda")
+    if args.config == 5:
+        K[:, :, ::64] *= 8.0
+    O, dQ, dK, dV = (torch.empty(shape, device="cuda") for _ in range(4))
+    LSE, D = (torch.empty((B, H, N), device="cuda") for _ in range(2))
+    ws = torch.empty(4 * B * H * N * 256 + 512, dtype=torch.uint8, device="cuda")
+    drop = dict(dropout_p=p, philox_seed=0x5EED0000 + rank, philox_offset=0) if p > 0 else {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # > 126 MB of L2
+    stream = torch.cuda.current_stream()
+
+    def step():
+        hk.attention_forward(Q, K, V, 0.125, causal, workspace=ws, out=O, lse=LSE, **drop)
+        hk.attention_backward(Q, K, V, O, dO, LSE, 0.125, causal, workspace=ws, D=D, dQ=dQ, dK=dK, dV=dV, **drop)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step()
+    barrier()
+    assert hk.last_device_status() == 0, "a bounded wait inside a kernel gave up during warm-up"
+
+    # ---- device-resident timing -------------------------------------------------
+    clocks = ClockSampler(local_rank)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    L.hk_attn_kernel_timing_enable(1)
+    n0 = hk.launch_count()
+    barrier()
+    clocks.start()  # sampled from here to the end of the end-to-end loop
+    t_wall = time.perf_counter()
+    for a, b in ev:
+        flush.zero_()  # L2 flush between timed iterations (untimed)
+        a.record(stream)
+        step()
+        b.record(stream)
+    barrier()
+    t_wall = time.perf_counter() - t_wall
+    launches = hk.launch_count() - n0
+    L.hk_attn_kernel_timing_enable(0)
+    ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
+    kt = {}
+    for kind, name in ((0, "fwd"), (1, "bwd")):
+        tot, n = C.c_double(), C.c_int()
+        L.hk_attn_kernel_timing_read(kind, C.byref(tot), C.byref(n))
+        kt[name] = tot.value / max(n.value, 1)
+    assert hk.last_device_status() == 0, "a bounded wait inside a kernel gave up"
+
+    # ---- end to end through the C ABI with host buffers ----------------------------
+    hQ, hK, hV, hdO = (t.cpu().pin_memory() for t in (Q, K, V, dO))
+    hO, hdQ, hdK, hdV = (torch.empty(shape).pin_memory() for _ in range(4))
+    hLSE = torch.empty((B, H, N)).pin_memory()
+    h2d = 4 * Q.numel() * 4
+    d2h = 4 * Q.numel() * 4 + LSE.numel() * 4
+
+    def e2e_step():
+        Q.copy_(hQ, non_blocking=True); K.copy_(hK, non_blocking=True)
+        V.copy_(hV, non_blocking=True); dO.copy_(hdO, non_blocking=True)
+        step()
+        hO.copy_(O, non_blocking=True); hLSE.copy_(LSE, non_blocking=True)
+        hdQ.copy_(dQ, non_blocking=True); hdK.copy_(dK, non_blocking=True); hdV.copy_(dV, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in ev2:
+        a.record(stream)
+        e2e_step()
+        b.record(stream)
+    barrier()
+    ms_e2e = sum(a.elapsed_time(b) for a, b in ev2) / args.steps
+    clk = clocks.stop()
+
+    if dist is not None:
+        t = torch.tensor([ms, ms_e2e, kt["fwd"], kt["bwd"]], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e, kt["fwd"], kt["bwd"] = (float(x) for x in t.tolist())
+    if rank == 0:
+        peaks = measured_peaks()
+        total = flops(cfg) * world
+        f_bwd = flops(cfg, fwd=False)
+        achieved = f_bwd / (kt["bwd"] * 1e-3) / 1e12 if kt["bwd"] > 0 else None
+        line = {
+            "metric": METRIC, "value": total / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+            "config": {"workload": cfg["name"] + (" per GPU" if world > 1 else ""), "config_id": args.config,
+                       "l2": "256 MiB buffer written between timed steps (untimed)",
+                       "step": "hk_attn_forward + hk_attn_backward (rounding pre-pass, D pre-pass, dQ zeroing, main kernels)",
+                       "partition": "batch x head across GPUs, no collective"},
+            "pct_of_tf32_peak": total / world / (ms * 1e-3) / 1e12 / peaks["tf32_tflops"],
+            "kernel_ms": {"fwd_kernel": kt["fwd"], "bwd_kernel": kt["bwd"],
+                          "fwd_kernel_tflops": flops(cfg, bwd=False) / (kt["fwd"] * 1e-3) / 1e12 if kt["fwd"] else None,
+                          "bwd_kernel_tflops": achieved},
+            "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel", "achieved": achieved,
+                         "peak": peaks["tf32_tflops"], "unit": "TFLOP/s",
+                         "frac": (achieved / peaks["tf32_tflops"]) if achieved else None,
+                         "peak_source": peaks["source"], "traffic": NCU_TRAFFIC_BYTES.get(args.config)},
+            "e2e": {"value": total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+            "gpu_launches": int(launches),
+            "clocks": clk,
+            "wall_s_timed_region": t_wall,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(cfg)
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    cfg = CONFIGS[args.config]
+    if args.impl == "reference":
+        run_reference(args, cfg, rank, world)
+    else:
+        run_ours(args, cfg, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

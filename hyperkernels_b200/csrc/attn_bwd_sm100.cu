@@ -381,8 +381,10 @@ int launch_attn_bwd(const BwdMaps& m, const BwdArgs& a, cudaStream_t stream) {
     }
     const long long nblocks = (long long)a.n_kvtiles * a.BH;
     if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
+    timing_mark(TIMED_BWD, true, stream);
     attn_bwd_kernel<<<(unsigned)nblocks, bwd::NUM_THREADS, bwd::SMEM_BYTES, stream>>>(m.q, m.k, m.v, m.dO, m.q_mn, m.k_mn,
                                                                                        m.dO_mn, a);
+    timing_mark(TIMED_BWD, false, stream);
     count_launch();
     return check_launch();
 }

@@ -42,6 +42,11 @@ int make_tile_map(CUtensorMap* map, const float* ptr, int inner, int B, int H, i
 
 DeviceStatus* device_status_ptr();  // per-device status word (allocated as a __device__ symbol)
 void count_launch(int n = 1);
+
+// Optional per-kernel timing (hk_attn_kernel_timing_enable): CUDA events recorded on
+// the launching stream around the two tensor-core kernels.
+enum TimedKernel { TIMED_FWD = 0, TIMED_BWD = 1, TIMED_KINDS = 2 };
+void timing_mark(int kind, bool begin, cudaStream_t stream);
 int check_launch();  // cudaGetLastError -> hk_status
 
 }  // namespace hk

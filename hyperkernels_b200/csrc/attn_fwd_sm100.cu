@@ -323,7 +323,9 @@ int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     }
     const long long nblocks = (long long)a.n_qtiles * a.BH;
     if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
+    timing_mark(TIMED_FWD, true, stream);
     attn_fwd_kernel<<<(unsigned)nblocks, fwd::NUM_THREADS, fwd::SMEM_BYTES, stream>>>(mq, mk, mv, a);
+    timing_mark(TIMED_FWD, false, stream);
     count_launch();
     return check_launch();
 }

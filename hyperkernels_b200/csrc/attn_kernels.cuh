@@ -55,5 +55,6 @@ struct BwdMaps {
 int launch_attn_bwd(const BwdMaps& m, const BwdArgs& a, cudaStream_t stream);
 
 int run_umma_selftest(int which, const float* A, const float* B, float* out, cudaStream_t stream);
+int run_umma_peak(int mode, int iters, int ctas, const float* A, const float* B, double* flops_out, cudaStream_t stream);
 
 }  // namespace hk

@@ -6,6 +6,7 @@
 #include <cstddef>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "attn_kernels.cuh"
 #include "attn_prepass.cuh"
@@ -33,6 +34,25 @@ namespace hk {
 // ---- process-wide state ------------------------------------------------------
 static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// ---- optional kernel timing -----------------------------------------------------
+static std::atomic<int> g_timing_on{0};
+static std::mutex g_timing_mu;
+struct EventPair { cudaEvent_t a, b; };
+static std::vector<EventPair> g_events[TIMED_KINDS];
+
+void timing_mark(int kind, bool begin, cudaStream_t stream) {
+    if (!g_timing_on.load(std::memory_order_relaxed)) return;
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    if (begin) {
+        EventPair e{};
+        if (cudaEventCreate(&e.a) != cudaSuccess || cudaEventCreate(&e.b) != cudaSuccess) return;
+        cudaEventRecord(e.a, stream);
+        g_events[kind].push_back(e);
+    } else if (!g_events[kind].empty()) {
+        cudaEventRecord(g_events[kind].back().b, stream);
+    }
+}
 
 int check_launch() { return cudaGetLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA; }
 
@@ -108,6 +128,28 @@ const char* hk_status_string(int s) {
         case HK_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
         default: return "unknown status";
     }
+}
+
+void hk_attn_kernel_timing_enable(int on) { g_timing_on.store(on ? 1 : 0); }
+
+int hk_attn_kernel_timing_read(int kind, double* total_ms, int* launches) {
+    if (kind < 0 || kind >= TIMED_KINDS || !total_ms || !launches) return HK_ERR_BAD_SHAPE;
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    double tot = 0;
+    int n = 0;
+    for (EventPair& e : g_events[kind]) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(e.b) == cudaSuccess && cudaEventElapsedTime(&ms, e.a, e.b) == cudaSuccess) {
+            tot += ms;
+            ++n;
+        }
+        cudaEventDestroy(e.a);
+        cudaEventDestroy(e.b);
+    }
+    g_events[kind].clear();
+    *total_ms = tot;
+    *launches = n;
+    return HK_OK;
 }
 
 uint64_t hk_attn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -367,6 +409,10 @@ int hk_attn_merge_partial(float* O_acc, float* LSE_acc, const float* O_part, con
 
 int hk_attn_selftest(int which, const float* A, const float* B, float* out, void* stream_) {
     return run_umma_selftest(which, A, B, out, static_cast<cudaStream_t>(stream_));
+}
+
+int hk_attn_mma_peak(int mode, int iters, int ctas, const float* A, const float* B, double* flops_out, void* stream_) {
+    return run_umma_peak(mode, iters, ctas, A, B, flops_out, static_cast<cudaStream_t>(stream_));
 }
 
 }  // extern "C"

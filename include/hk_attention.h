@@ -187,11 +187,27 @@ int hk_attn_last_device_status(void);
 /* Number of kernels this library has launched in this process (all devices). */
 uint64_t hk_attn_launch_count(void);
 
+/* Per-kernel timing for benchmarks: while enabled, CUDA events are recorded on the
+ * launching stream around the forward (kind 0) and backward (kind 1) tensor-core
+ * kernels; _read waits for them, returns their summed duration and count since
+ * the last read, and releases them.  The reference has no counterpart (its
+ * timing lives in its benchmark programs, blas/tests/test_sgemm_addmm_sm89.cu:131-145). */
+void hk_attn_kernel_timing_enable(int on);
+int hk_attn_kernel_timing_read(int kind, double* total_ms, int* launches);
+
 /* Runs the tensor-core self-test on the current device: small TF32 products
  * through each operand path the attention kernels use (K-major and MN-major
  * shared-memory operands, tensor-memory A operand).  out[0..n) receives the
  * raw results of case `which`; see hyperkernels_b200/csrc/umma_selftest.cu. */
 int hk_attn_selftest(int which, const float* A, const float* B, float* out, void* stream);
+
+/* Tensor-pipe throughput probe: `ctas` CTAs each issue `iters` groups of the TF32
+ * MMA shapes the attention kernels use (mode 0: S = Q K^T shape, 1: O = P V shape,
+ * 2: dQ = dS K shape, 3: mode 0 on two alternating accumulators, 4: M128 N256),
+ * back to back.  A and B are device [128,64] fp32 matrices.  *flops_out receives
+ * the operation count of the launch; time it with events on `stream`.  No
+ * counterpart in the reference. */
+int hk_attn_mma_peak(int mode, int iters, int ctas, const float* A, const float* B, double* flops_out, void* stream);
 
 const char* hk_status_string(int status);
 

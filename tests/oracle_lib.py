@@ -124,3 +124,46 @@ def rel_l2(a, b):
     den = float(np.linalg.norm(b.astype(np.float64)))
     num = float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)))
     return num / den if den > 0 else num
+
+
+# ---- per-head parallel drivers (ctypes releases the GIL; one (b,h) slice per call) ----
+def _pool():
+    import concurrent.futures as cf
+
+    return cf.ThreadPoolExecutor(max_workers=max(1, os.cpu_count() or 1))
+
+
+def attn_forward_mt(Q, K, V, scale, causal, mask=None, q_pos0=0, k_pos0=0):
+    B, H, Tq, Hd = Q.shape
+    O = np.empty((B, H, Tq, Hd), np.float32)
+    LSE = np.empty((B, H, Tq), np.float32)
+
+    def one(i):
+        b, h = divmod(i, H)
+        m = mask[i:i + 1] if mask is not None else None
+        o, l = attn_forward(Q[b:b + 1, h:h + 1], K[b:b + 1, h:h + 1], V[b:b + 1, h:h + 1], scale, causal, m, q_pos0, k_pos0)
+        O[b, h], LSE[b, h] = o[0, 0], l[0, 0]
+
+    with _pool() as ex:
+        list(ex.map(one, range(B * H)))
+    return O, LSE
+
+
+def attn_backward_mt(Q, K, V, O, dO, LSE, scale, causal, mask=None, q_pos0=0, k_pos0=0):
+    B, H, Tq, Hd = Q.shape
+    Tk = K.shape[2]
+    D = np.empty((B, H, Tq), np.float32)
+    dQ = np.empty((B, H, Tq, Hd), np.float32)
+    dK = np.empty((B, H, Tk, Hd), np.float32)
+    dV = np.empty((B, H, Tk, Hd), np.float32)
+
+    def one(i):
+        b, h = divmod(i, H)
+        m = mask[i:i + 1] if mask is not None else None
+        s = (slice(b, b + 1), slice(h, h + 1))
+        d, dq, dk, dv = attn_backward(Q[s], K[s], V[s], O[s], dO[s], LSE[s], scale, causal, m, q_pos0, k_pos0)
+        D[b, h], dQ[b, h], dK[b, h], dV[b, h] = d[0, 0], dq[0, 0], dk[0, 0], dv[0, 0]
+
+    with _pool() as ex:
+        list(ex.map(one, range(B * H)))
+    return D, dQ, dK, dV

@@ -1,0 +1,418 @@
+"""GPU parity tests: the sm_100a kernels, called through the C ABI, against the
+CPU oracle on identical seeded inputs.
+
+Gate (fp32 I/O, TF32 multiplies): max abs error <= 5e-3 and relative L2 error
+<= 1e-3 on O, dQ, dK, dV versus the oracle; LSE within 2e-3 absolute; the
+reference test's own, looser, peak-relative tolerances (kernels_test.cu:535-537,
+589-593) are asserted as well on the reference test's shape.  The dropout
+keep-mask is compared bit for bit.
+"""
+import numpy as np
+import pytest
+import torch
+
+import hyperkernels_b200 as hk
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, REL_L2, LSE_ABS = 5e-3, 1e-3, 2e-3
+SCALE = 0.125
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+def gate(name, got, ref, max_abs=MAX_ABS, rel=REL_L2):
+    """max-abs gate always; relative-L2 gate whenever the oracle tensor is not itself numerical noise
+    (with a single visible key dS = p (dP - D) is exactly 0 in real arithmetic, so dQ and dK of such a
+    case are pure rounding residue on both sides: RMS below 1e-3 is judged by max-abs only)."""
+    assert not np.isnan(got).any(), name
+    ma, rl = ol.max_abs(got, ref), ol.rel_l2(got, ref)
+    assert ma <= max_abs, f"{name}: max abs {ma:.3e} > {max_abs}"
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2))) if ref.size else 0.0
+    if rms >= 1e-3:
+        assert rl <= rel, f"{name}: rel L2 {rl:.3e} > {rel}"
+
+
+def lse_check(got, ref, tol=LSE_ABS):
+    """-inf (fully masked / fully dropped rows) must match exactly, the rest within tol."""
+    fin = np.isfinite(ref)
+    assert np.array_equal(np.isfinite(got), fin)
+    assert np.array_equal(got[~fin], ref[~fin])
+    assert ol.max_abs(got[fin], ref[fin]) <= tol
+
+
+def ok_status():
+    torch.cuda.synchronize()
+    assert hk.last_device_status() == 0
+
+
+def normal(shape, seed, sigma=1.0):
+    return (np.random.default_rng(seed).standard_normal(shape) * sigma).astype(np.float32)
+
+
+def run_fwd_bwd_check(Q, K, V, dO, causal, mask=None, fwd_kw=None, bwd_kw=None, q_pos0=0, k_pos0=0, chained=False):
+    """Forward vs oracle; backward fed the ORACLE's O/LSE (the reference tests the backward in isolation,
+    kernels_test.cu:559-561) unless chained."""
+    fwd_kw, bwd_kw = dict(fwd_kw or {}), dict(bwd_kw or {})
+    O_ref, L_ref = ol.attn_forward_mt(Q, K, V, SCALE, causal, mask, q_pos0, k_pos0)
+    D_ref, dQ_ref, dK_ref, dV_ref = ol.attn_backward_mt(Q, K, V, O_ref, dO, L_ref, SCALE, causal, mask, q_pos0, k_pos0)
+    tQ, tK, tV, tdO = dev(Q), dev(K), dev(V), dev(dO)
+    O, LSE = hk.attention_forward(tQ, tK, tV, SCALE, causal, q_pos0=q_pos0, k_pos0=k_pos0, **fwd_kw)
+    ok_status()
+    gate("O", host(O), O_ref)
+    lse_check(host(LSE), L_ref)
+    Oin, Lin = (O, LSE) if chained else (dev(O_ref), dev(L_ref))
+    dQ, dK, dV, D = hk.attention_backward(tQ, tK, tV, Oin, tdO, Lin, SCALE, causal, q_pos0=q_pos0, k_pos0=k_pos0, **bwd_kw)
+    ok_status()
+    gate("D", host(D), D_ref, max_abs=2e-2 if chained else 1e-4, rel=1e-3 if chained else 1e-5)
+    gate("dQ", host(dQ), dQ_ref)
+    gate("dK", host(dK), dK_ref)
+    gate("dV", host(dV), dV_ref)
+    return dict(O=host(O), LSE=host(LSE), dQ=host(dQ), dK=host(dK), dV=host(dV), refs=(O_ref, L_ref, dQ_ref, dK_ref, dV_ref))
+
+
+# ---------------------------------------------------------------------------
+# the reference's own test: B=2,H=6,T=256, uniform[-1,1] from mt19937_64 seeds 101..104
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("causal", [0, 1])
+def test_reference_test_shape(causal):
+    B, H, T = 2, 6, 256
+    n = B * H * T * 64
+    Q, K, V, dO = (ol.rand_vec(n, s).reshape(B, H, T, 64) for s in (101, 102, 103, 104))
+    r = run_fwd_bwd_check(Q, K, V, dO, causal)
+    O_ref, L_ref, dQ_ref, dK_ref, dV_ref = r["refs"]
+    # the reference's peak-relative tolerances (kernels_test.cu:535-537, 589-593)
+    assert ol.max_abs(r["O"], O_ref) <= max(2e-3, 0.04 * np.abs(O_ref).max())
+    assert ol.max_abs(r["LSE"], L_ref) <= max(2e-3, 0.02 * np.abs(L_ref).max())
+    for k, ref in (("dQ", dQ_ref), ("dK", dK_ref), ("dV", dV_ref)):
+        assert ol.max_abs(r[k], ref) <= max(2e-3, 0.08 * np.abs(ref).max())
+
+
+@pytest.mark.parametrize("name", ["attn_ref_T256", "attn_ref_T77"])
+@pytest.mark.parametrize("causal", [0, 1])
+def test_against_golden_vectors(name, causal):
+    import os
+
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name + ".npz"))
+    B, H, T, Hd, *seeds = [int(x) for x in g["meta"]]
+    n = B * H * T * 64
+    Q, K, V, dO = (dev(ol.rand_vec(n, s).reshape(B, H, T, 64)) for s in seeds)
+    O, LSE = hk.attention_forward(Q, K, V, SCALE, causal)
+    gate("O", host(O), g[f"O_causal{causal}"])
+    assert ol.max_abs(host(LSE), g[f"LSE_causal{causal}"]) <= LSE_ABS
+    dQ, dK, dV, D = hk.attention_backward(Q, K, V, dev(g[f"O_causal{causal}"]), dO, dev(g[f"LSE_causal{causal}"]), SCALE, causal)
+    ok_status()
+    gate("D", host(D), g[f"D_causal{causal}"], 1e-4, 1e-5)
+    for k, t in (("dQ", dQ), ("dK", dK), ("dV", dV)):
+        gate(k, host(t), g[f"{k}_causal{causal}"])
+
+
+# ---------------------------------------------------------------------------
+# BASELINE configs
+# ---------------------------------------------------------------------------
+def test_config1_B2_H4_N256_causal():
+    Q, K, V, dO = (normal((2, 4, 256, 64), s) for s in (0, 1, 2, 3))
+    run_fwd_bwd_check(Q, K, V, dO, 1)
+    run_fwd_bwd_check(Q, K, V, dO, 1, chained=True)
+
+
+def test_config2_gpt2_small_full():
+    """B=8,H=12,N=1024 causal, every head against the oracle (threads)."""
+    Q, K, V, dO = (normal((8, 12, 1024, 64), s) for s in (10, 11, 12, 13))
+    run_fwd_bwd_check(Q, K, V, dO, 1)
+
+
+def _subset_check(B, H, N, causal, p, sigma, heads, seed):
+    """Full-size run on the GPU; the listed (b,h) heads are checked against the oracle."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    Q, K, V = (torch.randn((B, H, N, 64), generator=g, device="cuda") * sigma for _ in range(3))
+    dO = torch.randn((B, H, N, 64), generator=g, device="cuda")
+    kw = dict(dropout_p=p, philox_seed=0x1234ABCD5678, philox_offset=42) if p > 0 else {}
+    O, LSE = hk.attention_forward(Q, K, V, SCALE, causal, **kw)
+    dQ, dK, dV, D = hk.attention_backward(Q, K, V, O, dO, LSE, SCALE, causal, **kw)
+    ok_status()
+    for (b, h) in heads:
+        q, k, v, g_ = (host(t[b:b + 1, h:h + 1]) for t in (Q, K, V, dO))
+        mask = _philox_mask_numpy(b * H + h, N, N, p, 0x1234ABCD5678, 42) if p > 0 else None
+        O_ref, L_ref = ol.attn_forward(q, k, v, SCALE, causal, mask)
+        D_ref, dQ_ref, dK_ref, dV_ref = ol.attn_backward(q, k, v, host(O[b:b + 1, h:h + 1]), g_, host(LSE[b:b + 1, h:h + 1]),
+                                                         SCALE, causal, mask)
+        gate("O", host(O[b:b + 1, h:h + 1]), O_ref)
+        lse_check(host(LSE[b:b + 1, h:h + 1]), L_ref)
+        gate("dQ", host(dQ[b:b + 1, h:h + 1]), dQ_ref)
+        gate("dK", host(dK[b:b + 1, h:h + 1]), dK_ref)
+        gate("dV", host(dV[b:b + 1, h:h + 1]), dV_ref)
+    return O, LSE, dQ, dK, dV, dO
+
+
+def _philox_mask_numpy(bh, Tq, Tk, p, seed, offset, q_pos0=0, k_pos0=0):
+    """Vectorised numpy Philox4x32-10, identical to csrc/philox.h (checked against it in test_dropout_mask_bit_exact)."""
+    M0, M1, W0, W1 = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85
+    qi = (np.arange(Tq, dtype=np.uint64) + q_pos0)[:, None]
+    k4 = ((np.arange((Tk + 3) // 4 + 1, dtype=np.uint64) + (k_pos0 >> 2)))[None, :]
+    c0 = np.broadcast_to(k4, (Tq, k4.shape[1])).astype(np.uint64)
+    c1 = np.broadcast_to(qi, c0.shape).astype(np.uint64)
+    c2 = np.full(c0.shape, bh, np.uint64)
+    c3 = np.full(c0.shape, offset & 0xFFFFFFFF, np.uint64)
+    k0 = seed & 0xFFFFFFFF
+    k1 = ((seed >> 32) ^ (offset >> 32)) & 0xFFFFFFFF
+    for _ in range(10):
+        p0 = c0 * np.uint64(M0)
+        p1 = c2 * np.uint64(M1)
+        hi0, lo0 = p0 >> np.uint64(32), p0 & np.uint64(0xFFFFFFFF)
+        hi1, lo1 = p1 >> np.uint64(32), p1 & np.uint64(0xFFFFFFFF)
+        n0 = hi1 ^ c1 ^ np.uint64(k0)
+        n2 = hi0 ^ c3 ^ np.uint64(k1)
+        c0, c1, c2, c3 = n0, lo1, n2, lo0
+        k0 = (k0 + W0) & 0xFFFFFFFF
+        k1 = (k1 + W1) & 0xFFFFFFFF
+    words = np.stack([c0, c1, c2, c3], axis=-1).reshape(Tq, -1)  # word index = 4*(k>>2 - k_pos0>>2) + (k&3)
+    start = k_pos0 & 3
+    words = words[:, start:start + Tk]
+    thr = min(int(np.float32(p).astype(np.float64) * 4294967296.0), 4294967295)
+    return (words >= np.uint64(thr)).astype(np.float32)[None]
+
+
+def test_config3_noncausal_dropout_subset():
+    """B=16,H=16,N=2048, p=0.1, sigma 0.5; 4 heads against the oracle, incl. first and last."""
+    _subset_check(16, 16, 2048, 0, 0.1, 0.5, [(0, 0), (7, 3), (15, 15), (3, 9)], seed=3)
+
+
+def test_config4_gpt2_xl_causal_dropout_subset():
+    """B=32,H=25,N=1024 causal p=0.1; 6 heads against the oracle."""
+    _subset_check(32, 25, 1024, 1, 0.1, 1.0, [(0, 0), (31, 24), (5, 7), (16, 12), (1, 1), (20, 3)], seed=4)
+
+
+# ---------------------------------------------------------------------------
+# edge cases: ragged lengths, tiny T, Tq != Tk, strided layouts, pre-rounded operands
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("T", [1, 5, 64, 127, 128, 129, 200, 333])
+@pytest.mark.parametrize("causal", [0, 1])
+def test_ragged_lengths(T, causal):
+    Q, K, V, dO = (normal((1, 3, T, 64), 100 + s + T) for s in range(4))
+    run_fwd_bwd_check(Q, K, V, dO, causal)
+
+
+@pytest.mark.parametrize("Tq,Tk", [(100, 300), (300, 100), (128, 1), (257, 513)])
+def test_different_query_and_key_lengths(Tq, Tk):
+    Q, dO = normal((2, 2, Tq, 64), 1), normal((2, 2, Tq, 64), 2)
+    K, V = normal((2, 2, Tk, 64), 3), normal((2, 2, Tk, 64), 4)
+    run_fwd_bwd_check(Q, K, V, dO, 0)
+
+
+@pytest.mark.parametrize("q_pos0,k_pos0,Tq,Tk", [(256, 0, 128, 384), (128, 128, 200, 200), (0, 128, 256, 128), (384, 256, 100, 260)])
+def test_causal_blocks_with_positions(q_pos0, k_pos0, Tq, Tk):
+    """A block of queries against a block of keys at global positions (ring-attention step);
+    rows that see no key in the block give O = 0, LSE = -inf."""
+    Q, dO = normal((1, 2, Tq, 64), 5), normal((1, 2, Tq, 64), 6)
+    K, V = normal((1, 2, Tk, 64), 7), normal((1, 2, Tk, 64), 8)
+    run_fwd_bwd_check(Q, K, V, dO, 1, q_pos0=q_pos0, k_pos0=k_pos0)
+
+
+def test_strided_bthd_layout_prerounded():
+    """[B,T,H,64] storage viewed as [B,H,T,64] (strideM > strideH), operands already TF32-representable:
+    the kernels read the caller's tensors directly through TMA, no workspace."""
+    B, H, T = 2, 3, 200
+    def tf32(x):
+        return ((x.view(np.uint32) + np.uint32(0x1000)) & np.uint32(0xFFFFE000)).view(np.float32)
+    Qs, Ks, Vs, dOs = (tf32(normal((B, T, H, 64), 30 + s)) for s in range(4))
+    Q, K, V, dO = (x.transpose(0, 2, 1, 3) for x in (Qs, Ks, Vs, dOs))  # numpy views [B,H,T,64]
+    O_ref, L_ref = ol.attn_forward_mt(np.ascontiguousarray(Q), np.ascontiguousarray(K), np.ascontiguousarray(V), SCALE, 1)
+    D_ref, dQ_ref, dK_ref, dV_ref = ol.attn_backward_mt(*(np.ascontiguousarray(x) for x in (Q, K, V)), O_ref,
+                                                         np.ascontiguousarray(dO), L_ref, SCALE, 1)
+    tQ, tK, tV, tdO = (dev(x).permute(0, 2, 1, 3) for x in (Qs, Ks, Vs, dOs))
+    out = torch.empty((B, T, H, 64), device="cuda").permute(0, 2, 1, 3)
+    O, LSE = hk.attention_forward(tQ, tK, tV, SCALE, 1, prerounded=True, out=out)
+    gate("O", host(O), O_ref)
+    dQ = torch.empty((B, T, H, 64), device="cuda").permute(0, 2, 1, 3)
+    dK = torch.empty((B, T, H, 64), device="cuda").permute(0, 2, 1, 3)
+    dV = torch.empty((B, T, H, 64), device="cuda").permute(0, 2, 1, 3)
+    tO = dev(O_ref)
+    hk.attention_backward(tQ, tK, tV, tO, tdO, dev(L_ref), SCALE, 1, prerounded=True, dQ=dQ, dK=dK, dV=dV)
+    ok_status()
+    gate("dQ", host(dQ), dQ_ref); gate("dK", host(dK), dK_ref); gate("dV", host(dV), dV_ref)
+
+
+def test_negative_scale_and_large_scores():
+    """Every 64th key row scaled x8 (the long-sequence config's stress of the running max), and a negative scale."""
+    Q, K, V, dO = (normal((1, 2, 512, 64), 40 + s) for s in range(4))
+    K[:, :, ::64] *= 8.0
+    O_ref, L_ref = ol.attn_forward_mt(Q, K, V, SCALE, 1)
+    O, LSE = hk.attention_forward(dev(Q), dev(K), dev(V), SCALE, 1)
+    # scores reach |s| ~ 60 here: TF32 product error grows with the operand magnitude, gate relative to it
+    assert ol.rel_l2(host(O), O_ref) <= 3e-3 and ol.max_abs(host(LSE), L_ref) <= 2e-2
+    O_ref2, L_ref2 = ol.attn_forward_mt(Q, normal((1, 2, 512, 64), 41), V, -SCALE, 0)
+    O2, L2 = hk.attention_forward(dev(Q), dev(normal((1, 2, 512, 64), 41)), dev(V), -SCALE, 0)
+    ok_status()
+    gate("O", host(O2), O_ref2)
+    assert ol.max_abs(host(L2), L_ref2) <= LSE_ABS
+
+
+# ---------------------------------------------------------------------------
+# dropout
+# ---------------------------------------------------------------------------
+def test_dropout_mask_bit_exact():
+    """Read the kernel's keep-mask out through the forward itself: Q = 0 makes every score equal, V = identity
+    makes O[i, j] = keep(i, k_pos0 + j) / (number kept), so O > 0 is the mask.  Compared bit for bit with the host
+    twin (hk_attn_dropout_mask) and with the numpy Philox used by the large-config tests."""
+    BH_B, BH_H, Tq = 2, 3, 200
+    seed, offset, p = 0xDEADBEEFCAFEF00D, 0x1_0000_0007, 0.1
+    Q = torch.zeros((BH_B, BH_H, Tq, 64), device="cuda")
+    eye = torch.eye(64, device="cuda").expand(BH_B, BH_H, 64, 64).contiguous()
+    K = torch.zeros((BH_B, BH_H, 64, 64), device="cuda")
+    host_mask = hk.dropout_keep_mask(BH_B * BH_H, Tq, 256, p, seed, offset, q_pos0=16, k_pos0=0)
+    assert np.array_equal(host_mask, ol.dropout_mask(BH_B * BH_H, Tq, 256, p, seed, offset, 16, 0))
+    for c in range(4):
+        O, _ = hk.attention_forward(Q, K, eye, SCALE, False, dropout_p=p, philox_seed=seed, philox_offset=offset,
+                                    q_pos0=16, k_pos0=64 * c)
+        got = (host(O) > 0).astype(np.float32).reshape(BH_B * BH_H, Tq, 64)
+        assert np.array_equal(got, host_mask[:, :, 64 * c:64 * c + 64]), c
+    ok_status()
+    for bh in (0, 5):
+        assert np.array_equal(_philox_mask_numpy(bh, Tq, 256, p, seed, offset, 16, 0)[0], host_mask[bh])
+    assert abs(host_mask.mean() - 0.9) < 0.01
+
+
+@pytest.mark.parametrize("causal", [0, 1])
+@pytest.mark.parametrize("mode", ["philox", "dense"])
+def test_dropout_forward_backward(causal, mode):
+    B, H, T, p, seed, off = 2, 2, 300, 0.25, 777, 12
+    Q, K, V, dO = (normal((B, H, T, 64), 50 + s) for s in range(4))
+    mask = ol.dropout_mask(B * H, T, T, p, seed, off)
+    if mode == "philox":
+        kw = dict(dropout_p=p, philox_seed=seed, philox_offset=off)
+    else:
+        kw = dict(dropout_p=p, dropout_mask=dev(mask))
+    r = run_fwd_bwd_check(Q, K, V, dO, causal, mask=mask, fwd_kw=kw, bwd_kw=kw)
+    if mode == "dense":
+        run_fwd_bwd_check(Q, K, V, dO, causal, mask=mask, fwd_kw=kw, bwd_kw=kw, chained=True)
+    assert r is not None
+
+
+def test_fully_dropped_row():
+    """Causal row 0 sees only key 0; when that key is dropped the reference gives O = 0, LSE = -inf
+    (fused_attn_forward_kernel_tc_sm89.cu:412,424) and the backward must treat the row as p = 0."""
+    B, H, T, p, seed = 1, 8, 64, 0.6, 5
+    mask = ol.dropout_mask(B * H, T, T, p, seed, 0)
+    dropped = [bh for bh in range(B * H) if mask[bh, 0, 0] == 0]
+    assert dropped, "pick another seed"
+    Q, K, V, dO = (normal((B, H, T, 64), 60 + s) for s in range(4))
+    kw = dict(dropout_p=p, philox_seed=seed, philox_offset=0)
+    r = run_fwd_bwd_check(Q, K, V, dO, 1, mask=mask, fwd_kw=kw, bwd_kw=kw, chained=True)
+    for bh in dropped:
+        assert np.all(r["O"][0, bh, 0] == 0) and r["LSE"][0, bh, 0] == -np.inf
+        assert np.all(r["dQ"][0, bh, 0] == 0)
+
+
+# ---------------------------------------------------------------------------
+# the other entry points
+# ---------------------------------------------------------------------------
+def test_precompute_D_reference_shape():
+    """kernels_test.cu:459-481: B=16, nh=12, T=1024, seeds 17/18, tolerance 2e-2 there."""
+    B, H, T = 16, 12, 1024
+    n = B * H * T * 64
+    dO, O = ol.rand_vec(n, 17).reshape(B, H, T, 64), ol.rand_vec(n, 18).reshape(B, H, T, 64)
+    p = hk.MemEfficientBwdParams()
+    tdO, tO = dev(dO), dev(O)
+    D = torch.empty((B, H, T), device="cuda")
+    p.dO, p.O, p.D = tdO.data_ptr(), tO.data_ptr(), D.data_ptr()
+    p.B, p.nh, p.T, p.scale = B, H, T, 1.0
+    p.do_strideB, p.do_strideH, p.do_strideM = H * T * 64, T * 64, 64
+    p.o_strideB, p.o_strideH, p.o_strideM = H * T * 64, T * 64, 64
+    p.d_strideB, p.d_strideH = H * T, T
+    hk.mem_efficient_bwd_precompute_D(p)
+    ok_status()
+    assert ol.max_abs(host(D), ol.precompute_D(dO, O)) <= 1e-4
+
+
+def test_backward_with_precomputed_D_and_accumulation():
+    B, H, T = 1, 2, 256
+    Q, K, V, dO = (normal((B, H, T, 64), 70 + s) for s in range(4))
+    O_ref, L_ref = ol.attn_forward_mt(Q, K, V, SCALE, 1)
+    D_ref, dQ_ref, dK_ref, dV_ref = ol.attn_backward_mt(Q, K, V, O_ref, dO, L_ref, SCALE, 1)
+    t = [dev(x) for x in (Q, K, V, O_ref, dO, L_ref)]
+    D = dev(D_ref)
+    base = torch.ones((B, H, T, 64), device="cuda")
+    dQ, dK, dV = base.clone(), base.clone() * 2, base.clone() * 3
+    hk.attention_backward(t[0], t[1], t[2], None, t[4], t[5], SCALE, 1, D=D, d_precomputed=True, accum_dq=True,
+                          accum_dkdv=True, dQ=dQ, dK=dK, dV=dV)
+    ok_status()
+    gate("dQ", host(dQ) - 1, dQ_ref); gate("dK", host(dK) - 2, dK_ref); gate("dV", host(dV) - 3, dV_ref)
+
+
+def test_merge_partial_equals_full():
+    """Keys split into two blocks, each attended separately, merged: equals attention over all keys."""
+    B, H, Tq, Tk = 2, 2, 200, 384
+    Q, K, V = normal((B, H, Tq, 64), 80), normal((B, H, Tk, 64), 81), normal((B, H, Tk, 64), 82)
+    O_ref, L_ref = ol.attn_forward_mt(Q, K, V, SCALE, 1, q_pos0=184)
+    tQ, tK, tV = dev(Q), dev(K), dev(V)
+    O, LSE = hk.attention_forward(tQ, tK[:, :, :256].contiguous(), tV[:, :, :256].contiguous(), SCALE, True, q_pos0=184, k_pos0=0)
+    O2, LSE2 = hk.attention_forward(tQ, tK[:, :, 256:].contiguous(), tV[:, :, 256:].contiguous(), SCALE, True, q_pos0=184, k_pos0=256)
+    hk.merge_partial(O, LSE, O2, LSE2)
+    ok_status()
+    gate("O", host(O), O_ref)
+    lse_check(host(LSE), L_ref)
+
+
+# ---------------------------------------------------------------------------
+# size-independent properties at full BASELINE sizes
+# ---------------------------------------------------------------------------
+def test_properties_gpt2_small_shape():
+    B, H, N = 8, 12, 1024
+    g = torch.Generator(device="cuda").manual_seed(9)
+    Q, K, dO = (torch.randn((B, H, N, 64), generator=g, device="cuda") for _ in range(3))
+    ones = torch.ones((B, H, N, 64), device="cuda")
+    # rows of P sum to 1: V = 1 gives O = 1
+    O, LSE = hk.attention_forward(Q, K, ones, SCALE, True)
+    assert float((O - 1).abs().max()) < 2e-3
+    # column sums of dV equal column sums of dO (sum_j dV_j = sum_i (sum_j p_ij) dO_i)
+    V = torch.randn((B, H, N, 64), generator=g, device="cuda")
+    O, LSE = hk.attention_forward(Q, K, V, SCALE, True)
+    dQ, dK, dV, D = hk.attention_backward(Q, K, V, O, dO, LSE, SCALE, True)
+    ok_status()
+    s_dv, s_do = dV.double().sum(2), dO.double().sum(2)
+    assert float((s_dv - s_do).abs().max()) < 5e-2 and float((s_dv - s_do).norm() / s_do.norm()) < 1e-3
+    # softmax shift invariance: sum_j dS_ij = 0, so dQ is unchanged by adding a constant vector to every key
+    c = torch.randn((1, 1, 1, 64), generator=g, device="cuda")
+    O2, LSE2 = hk.attention_forward(Q, K + c, V, SCALE, True)
+    dQ2, _, _, _ = hk.attention_backward(Q, K + c, V, O2, dO, LSE2, SCALE, True)
+    assert float((dQ2 - dQ).norm() / dQ.norm()) < 3e-3
+    # determinism of everything but the atomically accumulated dQ
+    dQ3, dK3, dV3, _ = hk.attention_backward(Q, K, V, O, dO, LSE, SCALE, True)
+    assert torch.equal(dK3, dK) and torch.equal(dV3, dV)
+    assert float((dQ3 - dQ).abs().max()) < 1e-4
+
+
+def test_long_sequence_rows_against_oracle():
+    """Long-sequence shape (N = 32768, every 64th key x8), 2 heads: the last 128 query rows, and the gradients of a
+    key block, against the oracle evaluated on just those rows / that block (position-addressed oracle)."""
+    H, N = 2, 32768
+    g = torch.Generator(device="cuda").manual_seed(11)
+    Q, K, V, dO = (torch.randn((1, H, N, 64), generator=g, device="cuda") for _ in range(4))
+    K[:, :, ::64] *= 8.0
+    O, LSE = hk.attention_forward(Q, K, V, SCALE, True)
+    dQ, dK, dV, D = hk.attention_backward(Q, K, V, O, dO, LSE, SCALE, True)
+    ok_status()
+    r0 = N - 128
+    O_ref, L_ref = ol.attn_forward_mt(host(Q[:, :, r0:]), host(K), host(V), SCALE, 1, q_pos0=r0)
+    # |scores| reach ~60 with the x8 keys: the TF32 product error scales with it (the reference kernel's does too)
+    assert ol.rel_l2(host(O[:, :, r0:]), O_ref) <= 3e-3
+    assert ol.max_abs(host(LSE[:, :, r0:]), L_ref) <= 2e-2
+    # dQ of those rows: needs every key
+    _, dQ_ref, _, _ = ol.attn_backward_mt(host(Q[:, :, r0:]), host(K), host(V), host(O[:, :, r0:]), host(dO[:, :, r0:]),
+                                          host(LSE[:, :, r0:]), SCALE, 1, q_pos0=r0)
+    assert ol.rel_l2(host(dQ[:, :, r0:]), dQ_ref) <= 5e-3
+    # dK, dV of key block [k0, k0+128): needs every query at or after k0
+    k0 = N - 2048
+    _, _, dK_ref, dV_ref = ol.attn_backward_mt(host(Q[:, :, k0:]), host(K[:, :, k0:k0 + 128]), host(V[:, :, k0:k0 + 128]),
+                                               host(O[:, :, k0:]), host(dO[:, :, k0:]), host(LSE[:, :, k0:]), SCALE, 1,
+                                               q_pos0=k0, k_pos0=k0)
+    assert ol.rel_l2(host(dK[:, :, k0:k0 + 128]), dK_ref) <= 5e-3
+    assert ol.rel_l2(host(dV[:, :, k0:k0 + 128]), dV_ref) <= 5e-3
