@@ -126,6 +126,8 @@ const char* hk_status_string(int s) {
         case HK_ERR_UNSUPPORTED: return "unsupported combination";
         case HK_ERR_CUDA: return "CUDA error";
         case HK_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
+        case HK_ERR_STATIC_SCRATCH:
+            return "problem needs more scratch than the 24 MiB built into the library; use hk_attn_forward with a workspace";
         default: return "unknown status";
     }
 }

@@ -45,8 +45,12 @@ typedef enum hk_status {
     HK_ERR_WORKSPACE = -5,     /* workspace missing or smaller than hk_attn_*_workspace_bytes */
     HK_ERR_UNSUPPORTED = -6,   /* combination the kernels do not implement */
     HK_ERR_CUDA = -7,          /* CUDA runtime/driver error (no device, launch failure) */
-    HK_ERR_DEVICE_TIMEOUT = -8 /* a bounded wait inside a kernel gave up */
+    HK_ERR_DEVICE_TIMEOUT = -8, /* a bounded wait inside a kernel gave up */
+    HK_ERR_STATIC_SCRATCH = -9  /* problem too large for the built-in scratch of hk_attn_forward_static_scratch */
 } hk_status;
+
+/* Size of the scratch array built into the library for hk_attn_forward_static_scratch. */
+#define HK_STATIC_SCRATCH_BYTES ((size_t)24 << 20)
 
 enum {
     /* dropout keep-mask is generated in the kernel from (dropout_seed, dropout_offset)
@@ -146,6 +150,20 @@ typedef struct hk_attn_bwd_params {
  * kernels/attention/fused_attn_forward_kernel_tc_sm89.cu:72-426).
  * Writes O and LSE.  `stream` is a cudaStream_t (NULL = default stream). */
 int hk_attn_forward(const hk_attn_fwd_params* p, void* stream);
+
+/* hk_attn_forward for callers that cannot allocate device memory (it has no
+ * counterpart in the reference, whose kernels need no scratch).  Same arguments
+ * and results as hk_attn_forward, but `workspace`/`workspace_bytes` are ignored:
+ * the TF32-rounded operand copies go into a 24 MiB array that is part of the
+ * library's device image, so the call itself allocates nothing (no cudaMalloc,
+ * no cudaFree).  Meant for plug-ins living inside a framework that owns all
+ * device memory, and for serving loops where an allocation would stall the GPU.
+ * Limits: B*nh*(T + 2*kv_len)*256 bytes must fit in HK_STATIC_SCRATCH_BYTES,
+ * otherwise HK_ERR_STATIC_SCRATCH; every GPU that loads the library carries the
+ * array until exit; all calls on a GPU share it, so calls that overlap in time
+ * on one GPU race (serialise them); the first call on each device resolves the
+ * array's address and should be made before any stream capture begins. */
+int hk_attn_forward_static_scratch(const hk_attn_fwd_params* p, void* stream);
 
 /* Replaces the launch of mem_efficient_bwd_precompute_D_sm89<64>
  * (kernels/tests/kernels_test.cu:475-477; kernel at
