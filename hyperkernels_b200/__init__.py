@@ -27,4 +27,5 @@ from .attention import (  # noqa: F401
     FLAG_ACCUM_DKDV,
     FLAG_ACCUM_DQ,
     FLAG_D_PRECOMPUTED,
+    FLAG_REUSE_FWD_ROUNDED,
 )

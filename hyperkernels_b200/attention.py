@@ -27,13 +27,16 @@ import ctypes as C
 import os
 from typing import Optional
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libhk_attention.so")
+# HK_ATTENTION_LIB overrides the location of the compiled library (e.g. an instrumented build).
+_LIB_PATH = os.environ.get("HK_ATTENTION_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib",
+                                                               "libhk_attention.so")
 
 FLAG_PHILOX_DROPOUT = 1 << 0
 FLAG_OPERANDS_PREROUNDED = 1 << 1
 FLAG_ACCUM_DKDV = 1 << 2
 FLAG_ACCUM_DQ = 1 << 3
 FLAG_D_PRECOMPUTED = 1 << 4
+FLAG_REUSE_FWD_ROUNDED = 1 << 5
 
 _f32p = C.POINTER(C.c_float)
 
@@ -247,7 +250,8 @@ def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float =
 def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropout_p: float = 0.0, dropout_mask=None,
                        philox_seed: Optional[int] = None, philox_offset: int = 0, q_pos0: int = 0, k_pos0: int = 0,
                        prerounded: bool = False, D=None, d_precomputed: bool = False, accum_dkdv: bool = False,
-                       accum_dq: bool = False, workspace=None, dQ=None, dK=None, dV=None, stream=None):
+                       accum_dq: bool = False, reuse_fwd_rounded: bool = False, workspace=None, dQ=None, dK=None, dV=None,
+                       stream=None):
     """dQ, dK, dV, D = fused attention backward (fp32 CUDA tensors, [B,H,T,64])."""
     import torch
 
@@ -286,6 +290,9 @@ def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropo
         flags |= FLAG_ACCUM_DKDV
     if accum_dq:
         flags |= FLAG_ACCUM_DQ
+    if reuse_fwd_rounded:
+        assert workspace is not None, "reuse_fwd_rounded needs the workspace the forward used"
+        flags |= FLAG_REUSE_FWD_ROUNDED
     p.flags = flags
     ws = _workspace(bwd_workspace_bytes(p), Q, workspace)
     if ws is not None:

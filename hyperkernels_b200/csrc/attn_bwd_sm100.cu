@@ -25,9 +25,14 @@
 // operand, which for TF32 must use the 32-byte-chunk swizzle), so TMA brings
 // each of them into shared memory twice, once per swizzle.  The K-major copies
 // of Q and dO are dead once S^T and dP^T are done, and dS is staged over them.
+// The MN-major copies are released as soon as dV and dK have consumed them, so
+// their reload overlaps dQ = dS K and its drain.
+//
 //   warp 0     TMA producer (K, V once; Q and dO per query tile)
 //   warp 1     MMA issuer
-//   warps 2-5  compute: thread r owns key row r (tensor-memory lane r)
+//   warps 2-17 compute: four threads per key row (tensor-memory lane), each
+//              owning 32 of the 128 query columns, all held in registers so
+//              that S^T and dP^T are read from tensor memory exactly once
 #include "attn_kernels.cuh"
 #include "philox.h"
 
@@ -35,7 +40,8 @@ namespace hk {
 
 namespace bwd {
 
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_COMPUTE = 512;
+constexpr int NUM_THREADS = 64 + NUM_COMPUTE;
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0;     // S^T, then P^T
 constexpr int COL_DP = 128;  // dP^T, then dS^T
@@ -44,9 +50,9 @@ constexpr int COL_DK = 320;
 constexpr int COL_DQ = 384;
 
 struct __align__(16) Shared {
-    float lse[TILE];   // LSE * log2e of the current query tile (+inf for rows past the end)
-    float dsum[TILE];  // D of the current query tile
-    uint64_t kv_full, qdo_full, qdo_empty, s_full, ds_ready, dq_full, dq_empty, staged;
+    float lse[2][TILE];   // LSE * log2e of the query tile (+inf for rows past the end), double-buffered
+    float dsum[2][TILE];  // D * scale of the query tile
+    uint64_t kv_full, qk_full, qk_empty, qm_full, qm_empty, s_full, ds_ready, dq_full, dq_empty, staged;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -60,10 +66,20 @@ constexpr int OFF_DS = OFF_QK;
 constexpr int OFF_QM = 5 * TILE_BYTES;   // Q, MN-major          (dK += dS^T Q)
 constexpr int OFF_DOM = 6 * TILE_BYTES;  // dO, MN-major         (dV += P^T dO)
 constexpr int OFF_SH = 7 * TILE_BYTES;
-constexpr int SMEM_BYTES = OFF_SH + sizeof(Shared) + 1024;
+// no slack for re-aligning the dynamic shared-memory base: it is declared 1024-byte aligned
+// and the kernel checks that it is (the 128-byte swizzles need it)
+constexpr int SMEM_BYTES = OFF_SH + sizeof(Shared);
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may opt in to");
 
-enum WaitId { W_KVFULL = 201, W_QDOFULL, W_QDOEMPTY, W_SFULL, W_DSREADY, W_DQFULL, W_DQEMPTY, W_STAGED };
+// Timeline slots (SM clock): role r in {0: MMA issuer, 1: compute thread 0}, iteration it, phase ph:
+// buffer[1 + (it * 2 + r) * 8 + ph]; buffer[0] = number of iterations of the recorded CTA.
+__device__ __forceinline__ void stamp(const BwdArgs& a, bool on, int it, int role, int ph) {
+    if (on && it < 200) a.timeline[1 + (it * 2 + role) * 8 + ph] = clock64();
+}
+
+enum WaitId {
+    W_KVFULL = 201, W_QKFULL, W_QKEMPTY, W_QMFULL, W_QMEMPTY, W_SFULL, W_DSREADY, W_DQFULL, W_DQEMPTY, W_STAGED
+};
 
 }  // namespace bwd
 
@@ -73,8 +89,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 const __grid_constant__ CUtensorMap mapQm, const __grid_constant__ CUtensorMap mapKm,
                 const __grid_constant__ CUtensorMap mapdOm, const BwdArgs a) {
     using namespace bwd;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {  // never expected; refuse to run on a misplaced buffer
+        if (threadIdx.x == 0 && atomicCAS(&a.status->code, 0, 299) == 0) a.status->block = blockIdx.x;
+        return;
+    }
     uint8_t* sK = smem + OFF_KK;
     uint8_t* sKm = smem + OFF_KM;
     uint8_t* sV = smem + OFF_V;
@@ -106,13 +125,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 
     if (threadIdx.x == 0) {
         mbar_init(&sh.kv_full, 1);
-        mbar_init(&sh.qdo_full, 1);
-        mbar_init(&sh.qdo_empty, 1);
+        mbar_init(&sh.qk_full, 1);
+        mbar_init(&sh.qk_empty, 1);
+        mbar_init(&sh.qm_full, 1);
+        mbar_init(&sh.qm_empty, 1);
         mbar_init(&sh.s_full, 1);
-        mbar_init(&sh.ds_ready, 128);
+        mbar_init(&sh.ds_ready, NUM_COMPUTE);
         mbar_init(&sh.dq_full, 1);
-        mbar_init(&sh.dq_empty, 128);
-        mbar_init(&sh.staged, 128);
+        mbar_init(&sh.dq_empty, 256);  // the two column groups that drain dQ
+        mbar_init(&sh.staged, 256);    // the threads that stage LSE and D
         sh.abort_flag = 0;
         fence_mbar_init();
     }
@@ -125,6 +146,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem = sh.tmem_base;
     WaitCtx wc{&sh.abort_flag, a.status};
+    const bool tl = a.timeline != nullptr && (int)blockIdx.x == a.timeline_block;
+    if (tl && threadIdx.x == 0) a.timeline[0] = n_it;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -139,29 +162,48 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             mbar_arrive_expect_tx(&sh.kv_full, 3 * TILE_BYTES);
             tma_load_4d(sK, &mapK, &sh.kv_full, 0, kv0, h, b);
             tma_load_4d(sK + BOX_BYTES, &mapK, &sh.kv_full, HALF_D, kv0, h, b);
-            tma_load_4d(sKm, &mapKm, &sh.kv_full, 0, kv0, h, b);
-            tma_load_4d(sKm + BOX_BYTES, &mapKm, &sh.kv_full, HALF_D, kv0, h, b);
             tma_load_4d(sV, &mapV, &sh.kv_full, 0, kv0, h, b);
             tma_load_4d(sV + BOX_BYTES, &mapV, &sh.kv_full, HALF_D, kv0, h, b);
-            int issued = 0;
+            tma_load_4d(sKm, &mapKm, &sh.kv_full, 0, kv0, h, b);
+            tma_load_4d(sKm + BOX_BYTES, &mapKm, &sh.kv_full, HALF_D, kv0, h, b);
+            int issued_k = 0, issued_m = 0;
             for (int it = 0; it < n_it; ++it) {
-                if (it > 0 && !mbar_wait(wc, &sh.qdo_empty, (it - 1) & 1, W_QDOEMPTY, it)) break;
                 const int q0 = (it0 + it) * TILE;
-                mbar_arrive_expect_tx(&sh.qdo_full, 4 * TILE_BYTES);
-                tma_load_4d(sQ, &mapQ, &sh.qdo_full, 0, q0, h, b);
-                tma_load_4d(sQ + BOX_BYTES, &mapQ, &sh.qdo_full, HALF_D, q0, h, b);
-                tma_load_4d(sdO, &mapdO, &sh.qdo_full, 0, q0, h, b);
-                tma_load_4d(sdO + BOX_BYTES, &mapdO, &sh.qdo_full, HALF_D, q0, h, b);
-                tma_load_4d(sQm, &mapQm, &sh.qdo_full, 0, q0, h, b);
-                tma_load_4d(sQm + BOX_BYTES, &mapQm, &sh.qdo_full, HALF_D, q0, h, b);
-                tma_load_4d(sdOm, &mapdOm, &sh.qdo_full, 0, q0, h, b);
-                tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qdo_full, HALF_D, q0, h, b);
-                issued = it + 1;
+                // K-major Q, dO (also the dS staging area: free once dQ of the previous tile is done)
+                if (it > 0 && !mbar_wait(wc, &sh.qk_empty, (it - 1) & 1, W_QKEMPTY, it)) break;
+                mbar_arrive_expect_tx(&sh.qk_full, 2 * TILE_BYTES);
+                tma_load_4d(sQ, &mapQ, &sh.qk_full, 0, q0, h, b);
+                tma_load_4d(sQ + BOX_BYTES, &mapQ, &sh.qk_full, HALF_D, q0, h, b);
+                tma_load_4d(sdO, &mapdO, &sh.qk_full, 0, q0, h, b);
+                tma_load_4d(sdO + BOX_BYTES, &mapdO, &sh.qk_full, HALF_D, q0, h, b);
+                issued_k = it + 1;
+                // MN-major Q, dO of the NEXT tile are requested below, ahead of time; the first tile's here
+                if (it == 0) {
+                    mbar_arrive_expect_tx(&sh.qm_full, 2 * TILE_BYTES);
+                    tma_load_4d(sQm, &mapQm, &sh.qm_full, 0, q0, h, b);
+                    tma_load_4d(sQm + BOX_BYTES, &mapQm, &sh.qm_full, HALF_D, q0, h, b);
+                    tma_load_4d(sdOm, &mapdOm, &sh.qm_full, 0, q0, h, b);
+                    tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qm_full, HALF_D, q0, h, b);
+                    issued_m = 1;
+                }
+                if (it + 1 < n_it) {
+                    // released right after dV/dK of tile `it`: reload overlaps dQ = dS K and its drain
+                    if (!mbar_wait(wc, &sh.qm_empty, it & 1, W_QMEMPTY, it)) break;
+                    const int q1 = q0 + TILE;
+                    mbar_arrive_expect_tx(&sh.qm_full, 2 * TILE_BYTES);
+                    tma_load_4d(sQm, &mapQm, &sh.qm_full, 0, q1, h, b);
+                    tma_load_4d(sQm + BOX_BYTES, &mapQm, &sh.qm_full, HALF_D, q1, h, b);
+                    tma_load_4d(sdOm, &mapdOm, &sh.qm_full, 0, q1, h, b);
+                    tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qm_full, HALF_D, q1, h, b);
+                    issued_m = it + 2;
+                }
             }
             // Do not leave the CTA while bulk copies into its shared memory are in flight.
             for (int i = 0; i < 100000 && !mbar_try_wait(&sh.kv_full, 0); ++i) {}
-            if (issued > 0)
-                for (int i = 0; i < 100000 && !mbar_try_wait(&sh.qdo_full, (issued - 1) & 1); ++i) {}
+            if (issued_k > 0)
+                for (int i = 0; i < 100000 && !mbar_try_wait(&sh.qk_full, (issued_k - 1) & 1); ++i) {}
+            if (issued_m > 0)
+                for (int i = 0; i < 100000 && !mbar_try_wait(&sh.qm_full, (issued_m - 1) & 1); ++i) {}
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
@@ -175,7 +217,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             bool ok = mbar_wait(wc, &sh.kv_full, 0, W_KVFULL);
             for (int it = 0; ok && it < n_it; ++it) {
                 const uint32_t par = it & 1;
-                if (!(ok = mbar_wait(wc, &sh.qdo_full, par, W_QDOFULL, it))) break;
+                stamp(a, tl, it, 0, 0);
+                if (!(ok = mbar_wait(wc, &sh.qk_full, par, W_QKFULL, it))) break;
+                stamp(a, tl, it, 0, 1);
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // S^T = K Q^T
@@ -186,7 +230,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     umma_ss_tf32(tmem + COL_DP, kmajor_desc(v_addr, kk, BOX_BYTES), kmajor_desc(do_addr, kk, BOX_BYTES),
                                  IDESC_ST, kk > 0);
                 umma_commit(&sh.s_full);
+                stamp(a, tl, it, 0, 2);
+                if (!(ok = mbar_wait(wc, &sh.qm_full, par, W_QMFULL, it))) break;
+                stamp(a, tl, it, 0, 3);
                 if (!(ok = mbar_wait(wc, &sh.ds_ready, par, W_DSREADY, it))) break;
+                stamp(a, tl, it, 0, 4);
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < TILE / 8; ++kk)  // dV += P^T dO
@@ -196,21 +244,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 for (int kk = 0; kk < TILE / 8; ++kk)  // dK += dS^T Q
                     umma_ts_tf32(tmem + COL_DK, tmem + COL_DP + kk * 8, mnmajor_desc(qm_addr, kk, BOX_BYTES), IDESC_TS,
                                  (it > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&sh.qm_empty);
+                stamp(a, tl, it, 0, 5);
                 if (it > 0 && !(ok = mbar_wait(wc, &sh.dq_empty, (it - 1) & 1, W_DQEMPTY, it))) break;
+                stamp(a, tl, it, 0, 6);
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < TILE / 8; ++kk)  // dQ = dS K
                     umma_ss_tf32(tmem + COL_DQ, mnmajor_desc(ds_addr, kk, BOX_BYTES), mnmajor_desc(km_addr, kk, BOX_BYTES),
                                  IDESC_DQ, kk > 0);
-                umma_commit(&sh.qdo_empty);
+                umma_commit(&sh.qk_empty);
                 umma_commit(&sh.dq_full);
+                stamp(a, tl, it, 0, 7);
             }
         }
     } else {
         // ------------------------------ compute ------------------------------
         const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;  // key row inside the tile = tensor-memory lane
-        const int tid = (warp - 2) * 32 + lane;  // 0..127 among the compute warps
+        const int part = (warp - 2) >> 2;       // which 32 of the 128 query columns this thread owns
+        const int row = quarter * 32 + lane;    // key row inside the tile = tensor-memory lane
+        const int tid = threadIdx.x - 64;       // 0..511 among the compute warps
+        const int c0 = part * 32;
         const int kvrow = kv0 + row;
         const bool kv_ok = kvrow < a.Tk;
         const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
@@ -219,30 +273,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         float* dq_bh = a.dQ + (int64_t)b * a.dq_sB + (int64_t)h * a.dq_sH;
         bool ok = true;
         uint32_t rs[32], rp[32];
+        const bool tlc = tl && tid == 0;
 
         for (int it = 0; it < n_it; ++it) {
             const int q0 = (it0 + it) * TILE;
-            {
-                const int q = q0 + tid;
-                float L = INFINITY, Dv = 0.f;
-                if (q < a.Tq) {
-                    const float l = __ldg(lse_bh + q);
-                    L = (l == -INFINITY) ? INFINITY : l * LOG2E;  // fully dropped row: every p is 0
-                    Dv = __ldg(d_bh + q);
+            stamp(a, tlc, it, 1, 0);
+            // stage LSE (threads 0..127) and D (threads 128..255) of this query tile into buffer it & 1.
+            // The buffer was last read two tiles ago; every compute thread passed that tile's ds_ready
+            // arrival long before this thread could get here (it has since waited on dq_full or s_full
+            // of the previous tile, which follow it).
+            if (tid < 2 * TILE) {
+                const int q = q0 + (tid & 127);
+                if (tid < TILE) {
+                    float L = INFINITY;
+                    if (q < a.Tq) {
+                        const float l = __ldg(lse_bh + q);
+                        L = (l == -INFINITY) ? INFINITY : l * LOG2E;  // fully dropped row: every p is 0
+                    }
+                    sh.lse[it & 1][tid] = L;
+                } else {
+                    sh.dsum[it & 1][tid - TILE] = (q < a.Tq) ? __ldg(d_bh + q) * a.scale : 0.f;
                 }
-                // safe to overwrite: every compute thread finished reading the previous
-                // tile's values before ds_ready, which the dq_full waited on above follows
-                sh.lse[tid] = L;
-                sh.dsum[tid] = Dv;
+                mbar_arrive(&sh.staged);
             }
             // an mbarrier rather than bar.sync: its wait is bounded, so a CTA that is
             // winding down after a failed wait cannot strand warps at a barrier
-            mbar_arrive(&sh.staged);
             ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.staged, it & 1, W_STAGED, it));
             if (!ok) break;
+            stamp(a, tlc, it, 1, 1);
             ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.s_full, it & 1, W_SFULL, it));
             if (!ok) break;
+            stamp(a, tlc, it, 1, 2);
             tc_fence_after_sync();
+
+            tmem_ld32(trow + COL_S + c0, rs);
+            tmem_ld32(trow + COL_DP + c0, rp);
 
             // first query column (local to the tile) this key row is visible to
             int cmin = 0;
@@ -252,109 +317,144 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             }
             if (!kv_ok) cmin = TILE;
 
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(trow + COL_S + c * 32, rs);
-                tmem_ld32(trow + COL_DP + c * 32, rp);
-                tmem_wait_ld();
-                uint32_t keep = 0xffffffffu;
-                if (a.dropout_mode == 2) {
-                    keep = 0u;
-                    const uint32_t kpos = (uint32_t)(a.k_pos0 + kvrow);
+            // dropout keep bits of this thread's 32 (query, key) pairs
+            uint32_t keep = 0xffffffffu;
+            if (a.dropout_mode == 2) {
+                keep = 0u;
+                const uint32_t kpos = (uint32_t)(a.k_pos0 + kvrow);
+                const uint32_t sel = kpos & 3u;
+#pragma unroll 4
+                for (int i = 0; i < 32; ++i) {
+                    hk_philox4_t w = hk_philox_row4(a.seed, a.offset, (uint32_t)bh, (uint32_t)(a.q_pos0 + q0 + c0 + i),
+                                                    kpos >> 2);
+                    const uint32_t word = sel == 0 ? w.v[0] : sel == 1 ? w.v[1] : sel == 2 ? w.v[2] : w.v[3];
+                    keep |= ((word >= a.drop_thr) ? 1u : 0u) << i;
+                }
+            } else if (a.dropout_mode == 1) {
+                keep = 0u;
+                if (kv_ok) {
 #pragma unroll 4
                     for (int i = 0; i < 32; ++i) {
-                        hk_philox4_t w = hk_philox_row4(a.seed, a.offset, (uint32_t)bh,
-                                                        (uint32_t)(a.q_pos0 + q0 + c * 32 + i), kpos >> 2);
-                        const uint32_t word = (kpos & 3u) == 0 ? w.v[0] : (kpos & 3u) == 1 ? w.v[1]
-                                              : (kpos & 3u) == 2 ? w.v[2] : w.v[3];
-                        keep |= (word >= a.drop_thr ? 1u : 0u) << i;
-                    }
-                } else if (a.dropout_mode == 1) {
-                    keep = 0u;
-                    if (kv_ok) {
-#pragma unroll 4
-                        for (int i = 0; i < 32; ++i) {
-                            const int q = q0 + c * 32 + i;
-                            if (q < a.Tq && __ldg(a.mask + ((size_t)bh * a.Tq + q) * (size_t)a.Tk + kvrow) != 0.f)
-                                keep |= 1u << i;
-                        }
+                        const int q = q0 + c0 + i;
+                        if (q < a.Tq && __ldg(a.mask + ((size_t)bh * a.Tq + q) * (size_t)a.Tk + kvrow) != 0.f)
+                            keep |= 1u << i;
                     }
                 }
-                uint32_t ds_bits[32];
+            }
+            // fold the causal / tail mask into the keep bits: column cc is visible iff cc >= cmin
+            {
+                const int lo = cmin - c0;  // first visible local index, may be <= 0 or >= 32
+                if (lo > 0) keep &= (lo >= 32) ? 0u : (0xffffffffu << lo);
+            }
+            tmem_wait_ld();
+            stamp(a, tlc, it, 1, 3);
+
+            // p = exp2(s*scale*log2e - LSE*log2e);  dS = p * (dP*scale - D*scale)
+            const float4* lse4 = reinterpret_cast<const float4*>(sh.lse[it & 1] + c0);
+            const float4* ds4 = reinterpret_cast<const float4*>(sh.dsum[it & 1] + c0);
+            if (keep == 0xffffffffu) {
+                // every pair visible and kept: no per-element integer work besides the two roundings
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int cc = c * 32 + i;
-                    float p = ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -sh.lse[cc]));
-                    if (cc < cmin || !((keep >> i) & 1u)) p = 0.f;
-                    const float ds = p * (__uint_as_float(rp[i]) - sh.dsum[cc]) * a.scale;
-                    rs[i] = tf32_round_bits(__float_as_uint(p));
-                    ds_bits[i] = tf32_round_bits(__float_as_uint(ds));
+                for (int g = 0; g < 8; ++g) {
+                    const float4 L = lse4[g];
+                    const float4 Dv = ds4[g];
+                    const float Ls[4] = {L.x, L.y, L.z, L.w};
+                    const float Ds[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const int i = g * 4 + t;
+                        const float p = ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -Ls[t]));
+                        const float ds = p * fmaf(__uint_as_float(rp[i]), a.scale, -Ds[t]);
+                        rs[i] = tf32_round_bits_mma(__float_as_uint(p));
+                        rp[i] = tf32_round_bits_mma(__float_as_uint(ds));
+                    }
                 }
-                tmem_st32(trow + COL_S + c * 32, rs);
-                tmem_st32(trow + COL_DP + c * 32, ds_bits);
-                // dS into shared memory (MN-major A operand of dQ = dS K): box c holds query
-                // columns 32c..32c+31, one 128-byte row per key row, 32-byte chunks
-                // XOR-swizzled with (row & 3)
-                uint8_t* drow = sdS + c * BOX_BYTES + row * 128;
+            } else {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float4 L = lse4[g];
+                    const float4 Dv = ds4[g];
+                    const float Ls[4] = {L.x, L.y, L.z, L.w};
+                    const float Ds[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const int i = g * 4 + t;
+                        float p = ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -Ls[t]));
+                        if (!((keep >> i) & 1u)) p = 0.f;
+                        const float ds = p * fmaf(__uint_as_float(rp[i]), a.scale, -Ds[t]);
+                        rs[i] = tf32_round_bits_mma(__float_as_uint(p));
+                        rp[i] = tf32_round_bits_mma(__float_as_uint(ds));
+                    }
+                }
+            }
+            tmem_st32(trow + COL_S + c0, rs);
+            tmem_st32(trow + COL_DP + c0, rp);
+            // dS into shared memory (MN-major A operand of dQ = dS K): box `part` holds query
+            // columns 32*part..32*part+31, one 128-byte row per key row, 32-byte chunks
+            // XOR-swizzled with (row & 3)
+            {
+                uint8_t* drow = sdS + part * BOX_BYTES + row * 128;
 #pragma unroll
                 for (int t = 0; t < 8; ++t) {
-                    uint4 v = make_uint4(ds_bits[4 * t], ds_bits[4 * t + 1], ds_bits[4 * t + 2], ds_bits[4 * t + 3]);
+                    uint4 v = make_uint4(rp[4 * t], rp[4 * t + 1], rp[4 * t + 2], rp[4 * t + 3]);
                     *reinterpret_cast<uint4*>(drow + ((((t >> 1) ^ (row & 3)) << 5) | ((t & 1) << 4))) = v;
                 }
             }
+            stamp(a, tlc, it, 1, 4);
             tmem_wait_st();
             fence_proxy_async_smem();
             tc_fence_before_sync();
             mbar_arrive(&sh.ds_ready);
+            stamp(a, tlc, it, 1, 5);
 
-            // drain dQ of this query tile (lane = query row)
-            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, it & 1, W_DQFULL, it));
-            if (!ok) break;
-            tc_fence_after_sync();
-            const int q = q0 + row;
-            float* dq_row = dq_bh + (int64_t)q * a.dq_sM;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                tmem_ld32(trow + COL_DQ + c * 32, rs);
+            // drain dQ of this query tile (lane = query row): column groups 0 and 1 take 32 columns each
+            if (part < 2) {
+                ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, it & 1, W_DQFULL, it));
+                if (!ok) break;
+                stamp(a, tlc, it, 1, 6);
+                tc_fence_after_sync();
+                const int q = q0 + row;
+                float* dq_row = dq_bh + (int64_t)q * a.dq_sM + part * 32;
+                tmem_ld32(trow + COL_DQ + part * 32, rs);
                 tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(&sh.dq_empty);  // dQ is in registers: the next dQ = dS K may overwrite tensor memory
                 if (q < a.Tq) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4)
-                        red_add_v4(dq_row + c * 32 + i, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]),
+                        red_add_v4(dq_row + i, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]),
                                    __uint_as_float(rs[i + 2]), __uint_as_float(rs[i + 3]));
                 }
+                stamp(a, tlc, it, 1, 7);
             }
-            tc_fence_before_sync();
-            mbar_arrive(&sh.dq_empty);
         }
 
-        // epilogue: dV and dK of this KV tile (the last dq_full covered every MMA issued)
+        // epilogue: dV and dK of this KV tile.  The last dq_full covered every MMA issued; column groups 2 and 3
+        // did not wait on it in the loop, so everybody waits here.  Groups 0,1 store dV, groups 2,3 store dK.
+        if (ok && n_it > 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (n_it - 1) & 1, W_DQFULL, n_it));
         tc_fence_after_sync();
-        float* dv_row = a.dV + (int64_t)b * a.dv_sB + (int64_t)h * a.dv_sH + (int64_t)kvrow * a.dv_sM;
-        float* dk_row = a.dK + (int64_t)b * a.dk_sB + (int64_t)h * a.dk_sH + (int64_t)kvrow * a.dk_sM;
-#pragma unroll 1
-        for (int t = 0; t < 4; ++t) {
-            const int col = (t < 2) ? COL_DV + t * 32 : COL_DK + (t - 2) * 32;
-            float* dst = ((t < 2) ? dv_row : dk_row) + (t & 1) * 32;
-            if (ok && n_it > 0) {
-                tmem_ld32(trow + col, rs);
-                tmem_wait_ld();
-            } else {
+        float* out_row = (part < 2)
+                             ? a.dV + (int64_t)b * a.dv_sB + (int64_t)h * a.dv_sH + (int64_t)kvrow * a.dv_sM + part * 32
+                             : a.dK + (int64_t)b * a.dk_sB + (int64_t)h * a.dk_sH + (int64_t)kvrow * a.dk_sM + (part - 2) * 32;
+        const int col = (part < 2) ? COL_DV + part * 32 : COL_DK + (part - 2) * 32;
+        if (ok && n_it > 0) {
+            tmem_ld32(trow + col, rs);
+            tmem_wait_ld();
+        } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) rs[i] = 0u;
-            }
-            if (kv_ok) {
+            for (int i = 0; i < 32; ++i) rs[i] = 0u;
+        }
+        if (kv_ok) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    float4 v = make_float4(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1]), __uint_as_float(rs[i + 2]),
-                                           __uint_as_float(rs[i + 3]));
-                    float4* d4 = reinterpret_cast<float4*>(dst + i);
-                    if (a.accum_dkdv) {
-                        const float4 o = *d4;
-                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                    }
-                    *d4 = v;
+            for (int i = 0; i < 32; i += 4) {
+                float4 v = make_float4(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1]), __uint_as_float(rs[i + 2]),
+                                       __uint_as_float(rs[i + 3]));
+                float4* d4 = reinterpret_cast<float4*>(out_row + i);
+                if (a.accum_dkdv) {
+                    const float4 o = *d4;
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
                 }
+                *d4 = v;
             }
         }
     }

@@ -19,6 +19,8 @@ struct FwdArgs {
     uint32_t drop_thr;
     uint64_t seed, offset;
     DeviceStatus* status;
+    long long* timeline;  // optional: per-phase SM clock stamps of one CTA (hk_attn_debug_timeline)
+    int timeline_block;
 };
 
 int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdArgs& a,
@@ -44,6 +46,8 @@ struct BwdArgs {
     uint32_t drop_thr;
     uint64_t seed, offset;
     DeviceStatus* status;
+    long long* timeline;  // optional: per-phase SM clock stamps of one CTA (hk_attn_debug_timeline)
+    int timeline_block;
 };
 
 // K-major maps (16-byte-chunk swizzle) of Q, K, V, dO and MN-major maps

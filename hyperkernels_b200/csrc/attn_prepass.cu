@@ -55,7 +55,8 @@ int launch_round_tf32(const RoundJob& job, cudaStream_t stream) {
 // D[b,h,i] = sum_k dO[i,k] * O[i,k]  (mem_efficient_bwd_precompute_D_sm89.cu:45-91),
 // 16 lanes per row, one float4 of each operand per lane.  Optionally also
 // writes the TF32-rounded copy of dO the backward MMAs consume, so dO is read
-// from HBM once.
+// from HBM once, and zeroes the matching rows of dQ (the reference leaves that
+// to its caller, kernels_test.cu:562).
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) precompute_D_kernel(const DJob j) {
     const long long nrows = (long long)j.BH * j.T;
@@ -81,6 +82,9 @@ __global__ void __launch_bounds__(256) precompute_D_kernel(const DJob j) {
                 y.w = tf32_round_bits(__float_as_uint(g.w));
                 reinterpret_cast<uint4*>(j.dO_rounded)[row * 16 + sub] = y;
             }
+            if (j.dQ_zero)
+                reinterpret_cast<float4*>(j.dQ_zero + (int64_t)b * j.dq_sB + (int64_t)h * j.dq_sH + (int64_t)r * j.dq_sM)[sub] =
+                    make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);

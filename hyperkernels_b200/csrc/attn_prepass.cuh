@@ -18,6 +18,8 @@ struct DJob {
     float* D;
     int64_t d_sB, d_sH;
     float* dO_rounded;  // contiguous [BH, T, 64] or nullptr
+    float* dQ_zero;     // if set: the same rows of dQ are zeroed on the way (dQ is accumulated with atomics)
+    int64_t dq_sB, dq_sM, dq_sH;
     int H, BH, T;
 };
 int launch_precompute_D(const DJob& j, cudaStream_t stream);

@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstddef>
+#include <cstdio>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -54,7 +55,12 @@ void timing_mark(int kind, bool begin, cudaStream_t stream) {
     }
 }
 
-int check_launch() { return cudaGetLastError() == cudaSuccess ? HK_OK : HK_ERR_CUDA; }
+int check_launch() {
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return HK_OK;
+    fprintf(stderr, "libhk_attention: kernel launch failed: %s\n", cudaGetErrorString(e));
+    return HK_ERR_CUDA;
+}
 
 __device__ DeviceStatus g_device_status;  // one instance per device that loads the module
 
@@ -103,6 +109,10 @@ int make_tile_map(CUtensorMap* map, const float* ptr, int inner, int B, int H, i
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? HK_OK : HK_ERR_CUDA;
 }
+
+// ---- optional phase timeline of one CTA (performance debugging) ------------------
+static long long* g_timeline = nullptr;
+static int g_timeline_block = 0;
 
 // ---- validation helpers -------------------------------------------------------
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -282,6 +292,8 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     a.seed = p->dropout_seed; a.offset = p->dropout_offset;
     a.status = device_status_ptr();
     if (!a.status) return HK_ERR_CUDA;
+    a.timeline = g_timeline;
+    a.timeline_block = g_timeline_block;
     return launch_attn_fwd(mq, mk, mv, a, stream);
 }
 
@@ -299,6 +311,7 @@ int hk_attn_bwd_precompute_D(const hk_attn_bwd_params* p, void* stream_) {
     j.O = View4{p->O, p->o_strideB, p->o_strideM, p->o_strideH};
     j.D = p->D; j.d_sB = p->d_strideB; j.d_sH = p->d_strideH;
     j.dO_rounded = nullptr;
+    j.dQ_zero = nullptr;
     j.H = p->nh; j.BH = p->B * p->nh; j.T = p->T;
     return launch_precompute_D(j, stream);
 }
@@ -344,18 +357,28 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
         const size_t need = hk_attn_bwd_workspace_bytes(p);
         if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u))
             return HK_ERR_WORKSPACE;
+        // layout: rounded Q, K, V exactly where hk_attn_forward puts them, then rounded dO
         uint8_t* ws = static_cast<uint8_t*>(p->workspace);
         const size_t qb = align_up((size_t)BH * Tq * 256, 256), kb = align_up((size_t)BH * Tk * 256, 256);
         float* qr = reinterpret_cast<float*>(ws);
-        dO_rounded = reinterpret_cast<float*>(ws + qb);
-        float* kr = reinterpret_cast<float*>(ws + 2 * qb);
-        float* vr = reinterpret_cast<float*>(ws + 2 * qb + kb);
+        float* kr = reinterpret_cast<float*>(ws + qb);
+        float* vr = reinterpret_cast<float*>(ws + qb + kb);
+        dO_rounded = reinterpret_cast<float*>(ws + qb + 2 * kb);
+        const bool reuse = (p->flags & HK_FLAG_REUSE_FWD_ROUNDED) != 0;
         RoundJob job{};
-        job.src[0] = vQ; job.src[1] = vK; job.src[2] = vV; job.src[3] = vdO;
-        job.dst[0] = qr; job.dst[1] = kr; job.dst[2] = vr; job.dst[3] = dO_rounded;
-        job.T[0] = (int)Tq; job.T[1] = (int)Tk; job.T[2] = (int)Tk; job.T[3] = (int)Tq;
         job.H = H; job.BH = BH;
-        job.n = d_given ? 4 : 3;  // otherwise the D pre-pass writes the rounded dO while it reads dO
+        int n = 0;
+        if (!reuse) {
+            job.src[0] = vQ; job.src[1] = vK; job.src[2] = vV;
+            job.dst[0] = qr; job.dst[1] = kr; job.dst[2] = vr;
+            job.T[0] = (int)Tq; job.T[1] = (int)Tk; job.T[2] = (int)Tk;
+            n = 3;
+        }
+        if (d_given) {  // otherwise the D pre-pass writes the rounded dO while it reads dO
+            job.src[n] = vdO; job.dst[n] = dO_rounded; job.T[n] = (int)Tq;
+            ++n;
+        }
+        job.n = n;
         if ((rc = launch_round_tf32(job, stream))) return rc;
         tQ = View4{qr, (int64_t)H * Tq * 64, 64, Tq * 64};
         tdO = View4{dO_rounded, (int64_t)H * Tq * 64, 64, Tq * 64};
@@ -374,11 +397,14 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
         j.dO = vdO; j.O = vO;
         j.D = p->D; j.d_sB = p->d_strideB; j.d_sH = p->d_strideH;
         j.dO_rounded = dO_rounded;
+        if (!(p->flags & HK_FLAG_ACCUM_DQ)) {
+            j.dQ_zero = p->dQ; j.dq_sB = p->dq_strideB; j.dq_sM = p->dq_strideM; j.dq_sH = p->dq_strideH;
+        }
         j.H = H; j.BH = BH; j.T = (int)Tq;
         if ((rc = launch_precompute_D(j, stream))) return rc;
-    }
-    if (!(p->flags & HK_FLAG_ACCUM_DQ))
+    } else if (!(p->flags & HK_FLAG_ACCUM_DQ)) {
         if ((rc = launch_zero_rows(p->dQ, p->dq_strideB, p->dq_strideM, p->dq_strideH, B, H, (int)Tq, stream))) return rc;
+    }
 
     BwdArgs a{};
     a.LSE = p->LSE; a.D = p->D; a.dQ = p->dQ; a.dK = p->dK; a.dV = p->dV;
@@ -398,6 +424,8 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     a.seed = p->dropout_seed; a.offset = p->dropout_offset;
     a.status = device_status_ptr();
     if (!a.status) return HK_ERR_CUDA;
+    a.timeline = g_timeline;
+    a.timeline_block = g_timeline_block;
     return launch_attn_bwd(m, a, stream);
 }
 
@@ -411,6 +439,11 @@ int hk_attn_merge_partial(float* O_acc, float* LSE_acc, const float* O_part, con
 
 int hk_attn_selftest(int which, const float* A, const float* B, float* out, void* stream_) {
     return run_umma_selftest(which, A, B, out, static_cast<cudaStream_t>(stream_));
+}
+
+void hk_attn_debug_timeline(long long* device_buffer, int block) {
+    g_timeline = device_buffer;
+    g_timeline_block = block;
 }
 
 int hk_attn_mma_peak(int mode, int iters, int ctas, const float* A, const float* B, double* flops_out, void* stream_) {

@@ -203,6 +203,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 
+// Pointer flavours for slices of a larger register array (indices must be
+// compile-time constants after unrolling so the array stays in registers).
+__device__ __forceinline__ void tmem_ld32p(uint32_t taddr, uint32_t* r) {
+    tmem_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(r));
+}
+__device__ __forceinline__ void tmem_st32p(uint32_t taddr, const uint32_t* r) {
+    tmem_st32(taddr, *reinterpret_cast<const uint32_t(*)[32]>(r));
+}
+
 // ---------------------------------------------------------------------------
 // tcgen05.mma, kind::tf32, one CTA
 // ---------------------------------------------------------------------------
@@ -302,6 +311,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // Round an fp32 bit pattern to TF32 the way the reference does before every
 // MMA (bits + 0x1000; the tensor core then ignores the low 13 bits).
 __device__ __forceinline__ uint32_t tf32_round_bits(uint32_t bits) { return (bits + 0x1000u) & 0xFFFFE000u; }
+// Same value as seen by the tensor core, which drops the low 13 bits itself:
+// for operands written by a kernel straight into tensor or shared memory.
+__device__ __forceinline__ uint32_t tf32_round_bits_mma(uint32_t bits) { return bits + 0x1000u; }
 
 __device__ __forceinline__ void red_add_v4(float* gptr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b), "f"(c), "f"(d)

@@ -66,7 +66,10 @@ enum {
     HK_FLAG_ACCUM_DQ = 1u << 3,
     /* backward: D is supplied by the caller (reference behaviour of the unified
      * kernel taken alone); otherwise hk_attn_backward computes it from dO and O. */
-    HK_FLAG_D_PRECOMPUTED = 1u << 4
+    HK_FLAG_D_PRECOMPUTED = 1u << 4,
+    /* backward: `workspace` is the one hk_attn_forward was given for these same Q, K, V
+     * (same shapes) and still holds their rounded copies: do not round them again. */
+    HK_FLAG_REUSE_FWD_ROUNDED = 1u << 5
 };
 
 /* ---- forward ------------------------------------------------------------
@@ -218,6 +221,12 @@ int hk_attn_kernel_timing_read(int kind, double* total_ms, int* launches);
  * shared-memory operands, tensor-memory A operand).  out[0..n) receives the
  * raw results of case `which`; see hyperkernels_b200/csrc/umma_selftest.cu. */
 int hk_attn_selftest(int which, const float* A, const float* B, float* out, void* stream);
+
+/* Performance debugging: while `device_buffer` (device memory, 4096 int64) is set, CTA
+ * number `block` of every forward/backward launch writes SM-clock stamps of its
+ * pipeline phases into it (slot layout in csrc/attn_*_sm100.cu).  NULL turns it off.
+ * No counterpart in the reference. */
+void hk_attn_debug_timeline(long long* device_buffer, int block);
 
 /* Tensor-pipe throughput probe: `ctas` CTAs each issue `iters` groups of the TF32
  * MMA shapes the attention kernels use (mode 0: S = Q K^T shape, 1: O = P V shape,

@@ -367,6 +367,22 @@ def test_backward_with_precomputed_D_and_accumulation():
     gate("dQ", host(dQ) - 1, dQ_ref); gate("dK", host(dK) - 2, dK_ref); gate("dV", host(dV) - 3, dV_ref)
 
 
+def test_backward_reuses_forward_rounded_operands():
+    """Same workspace for forward and backward: the backward skips re-rounding Q, K, V."""
+    B, H, T = 2, 3, 300
+    Q, K, V, dO = (normal((B, H, T, 64), 90 + s) for s in range(4))
+    O_ref, L_ref = ol.attn_forward_mt(Q, K, V, SCALE, 1)
+    D_ref, dQ_ref, dK_ref, dV_ref = ol.attn_backward_mt(Q, K, V, O_ref, dO, L_ref, SCALE, 1)
+    tQ, tK, tV, tdO = dev(Q), dev(K), dev(V), dev(dO)
+    ws = torch.empty(4 * B * H * T * 256 + 512, dtype=torch.uint8, device="cuda")
+    O, LSE = hk.attention_forward(tQ, tK, tV, SCALE, True, workspace=ws)
+    dQ, dK, dV, D = hk.attention_backward(tQ, tK, tV, O, tdO, LSE, SCALE, True, workspace=ws, reuse_fwd_rounded=True)
+    ok_status()
+    gate("O", host(O), O_ref); gate("dQ", host(dQ), dQ_ref); gate("dK", host(dK), dK_ref); gate("dV", host(dV), dV_ref)
+    dQ2, dK2, dV2, _ = hk.attention_backward(tQ, tK, tV, O, tdO, LSE, SCALE, True)
+    assert torch.equal(dK, dK2) and torch.equal(dV, dV2)
+
+
 def test_merge_partial_equals_full():
     """Keys split into two blocks, each attended separately, merged: equals attention over all keys."""
     B, H, Tq, Tk = 2, 2, 200, 384
