@@ -8,19 +8,25 @@
 // O = alpha*O + P V with P rounded to TF32, finally O /= l (0 if l == 0) and
 // LSE = m + log l (-inf if l == 0).
 //
-// Blackwell structure (one CTA = one 128-row query tile, two CTAs per SM):
-//   warp 0      TMA producer: Q once, then one K tile and one V tile per step,
-//               128-byte-swizzled boxes of 128 rows x 32 floats, mbarrier tx
-//               (V with the 32-byte-chunk swizzle an MN-major TF32 operand needs).
-//   warp 1      MMA issuer: S = Q K^T as 8 tcgen05.mma (M128 N128 K8, both
-//               operands from shared memory), O += P V as 16 tcgen05.mma
-//               (M128 N64 K8, A = P read from tensor memory, B = V MN-major
-//               from shared memory).  S (128 columns) and O (64 columns) live
-//               in tensor memory; P overwrites S in place.
-//   warps 2-5   softmax: thread r owns query row r (tensor-memory lane r), so
-//               the row max and row sum need no cross-thread reduction.
-// While one CTA's softmax warps work, the SM's other CTA keeps the tensor
-// pipe busy.
+// Blackwell structure: one CTA per 256 query rows = two 128-row tiles that take
+// turns on the tensor pipe, so that the softmax of one tile runs while the
+// MMAs of the other execute.
+//   warp 0        TMA producer: both Q tiles once, then K and V tiles through a
+//                 two-stage ring (128-byte-swizzled boxes of 128 rows x 32
+//                 floats, mbarrier tx; V with the 32-byte-chunk swizzle an
+//                 MN-major TF32 operand needs).
+//   warp 1        MMA issuer, in the order PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1):
+//                 S_t = Q_t K^T is 8 tcgen05.mma (M128 N128 K8, operands from
+//                 shared memory), O_t += P_t V is 16 (M128 N64 K8, A = P_t read
+//                 from tensor memory, B = V MN-major from shared memory).
+//   warps 4-7     softmax of tile 0, warps 8-11 softmax of tile 1: thread r owns
+//                 query row r (tensor-memory lane r), holds the 128 scores of a
+//                 step in registers (one tensor-memory read per score), writes P
+//                 back over S.  The running output is rescaled only when the
+//                 running maximum grew by more than 2^8 (the final O/l and LSE
+//                 use the same maximum, so the result is the same function).
+// Tensor memory: S_0, S_1 (128 columns each), O_0, O_1 (64 columns each).
+// Warps 0-3 give most of their registers to the softmax warps (setmaxnreg).
 #include "attn_kernels.cuh"
 #include "philox.h"
 
@@ -28,66 +34,92 @@ namespace hk {
 
 namespace fwd {
 
-constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 256;
-constexpr int COL_S = 0;
-constexpr int COL_O = 128;
+constexpr int NUM_THREADS = 384;
+constexpr int TMEM_COLS = 512;
+constexpr int COL_S0 = 0;    // S_t at COL_S0 + 128 t
+constexpr int COL_O0 = 256;  // O_t at COL_O0 + 64 t
+constexpr int NST = 2;       // K/V ring depth
+constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 struct __align__(8) Shared {
-    uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
+    uint64_t q_full, k_full[NST], k_empty[NST], v_full[NST], v_empty[NST], s_full[2], p_full[2], o_full[2];
     uint32_t tmem_base;
     int abort_flag;
 };
 
-constexpr int SMEM_TILES = 3 * TILE_BYTES;                      // Q, K, V
-constexpr int SMEM_BYTES = SMEM_TILES + sizeof(Shared) + 1024;  // + alignment slack
+constexpr int OFF_Q = 0;                          // two tiles
+constexpr int OFF_K = 2 * TILE_BYTES;             // NST stages
+constexpr int OFF_V = OFF_K + NST * TILE_BYTES;   // NST stages
+constexpr int OFF_SH = OFF_V + NST * TILE_BYTES;
+constexpr int SMEM_BYTES = OFF_SH + sizeof(Shared);
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may opt in to");
 
-enum WaitId {
-    W_QFULL = 101, W_KFULL, W_KEMPTY, W_VFULL, W_VEMPTY, W_SFULL, W_PFULL, W_OFULL
-};
+enum WaitId { W_QFULL = 101, W_KFULL, W_KEMPTY, W_VFULL, W_VEMPTY, W_SFULL, W_PFULL, W_OFULL };
 
-}  // namespace fwd
+// Timeline slots (SM clock): role 0 = MMA issuer, 1 = softmax thread 0 of tile 0, 2 = of tile 1;
+// buffer[1 + (j * 3 + role) * 8 + ph]; buffer[0] = number of KV steps of the recorded CTA.
+__device__ __forceinline__ void stamp(const FwdArgs& a, bool on, int j, int role, int ph) {
+    if (on && j < 150) a.timeline[1 + (j * 3 + role) * 8 + ph] = clock64();
+}
 
-__global__ void __launch_bounds__(fwd::NUM_THREADS, 2)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                const __grid_constant__ CUtensorMap mapV, const FwdArgs a) {
-    using namespace fwd;
-    extern __shared__ uint8_t smem_raw[];
-    // 128-byte-swizzled tiles need 1024-byte alignment
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sQ = smem;
-    uint8_t* sK = smem + TILE_BYTES;
-    uint8_t* sV = smem + 2 * TILE_BYTES;
-    Shared& sh = *reinterpret_cast<Shared*>(smem + SMEM_TILES);
+// 384 threads x 168 registers at launch = 128 x 48 + 256 x 224 after the hand-over
+__device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 48;\n"); }
+__device__ __forceinline__ void reg_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;\n"); }
 
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-
-    // heavy (late) query tiles first: under the causal mask they have the most key tiles
-    const int bh = blockIdx.x % a.BH;
-    const int qt = a.n_qtiles - 1 - (int)(blockIdx.x / a.BH);
-    const int b = bh / a.H;
-    const int h = bh - b * a.H;
-    const int q0 = qt * TILE;
-
-    // number of key tiles this query tile attends to
+// number of key tiles the 128-row query tile starting at local row q0 attends to
+__device__ __forceinline__ int kv_tiles_for(const FwdArgs& a, int q0) {
+    if (q0 >= a.Tq) return 0;
     int kv_end = a.Tk;
     if (a.causal) {
         const int last_row = min(q0 + TILE, a.Tq) - 1;
         const long long lim = (long long)a.q_pos0 + last_row - a.k_pos0 + 1;
         kv_end = (int)max(0ll, min((long long)a.Tk, lim));
     }
-    const int n_kv = (kv_end + TILE - 1) / TILE;
+    return (kv_end + TILE - 1) / TILE;
+}
+
+}  // namespace fwd
+
+__global__ void __launch_bounds__(fwd::NUM_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                const __grid_constant__ CUtensorMap mapV, const FwdArgs a) {
+    using namespace fwd;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0) {  // never expected; refuse to run on a misplaced buffer
+        if (threadIdx.x == 0 && atomicCAS(&a.status->code, 0, 199) == 0) a.status->block = blockIdx.x;
+        return;
+    }
+    uint8_t* sQ = smem + OFF_Q;
+    uint8_t* sK = smem + OFF_K;
+    uint8_t* sV = smem + OFF_V;
+    Shared& sh = *reinterpret_cast<Shared*>(smem + OFF_SH);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // heavy (late) query blocks first: under the causal mask they have the most key tiles
+    const int bh = blockIdx.x % a.BH;
+    const int qb = a.n_qtiles - 1 - (int)(blockIdx.x / a.BH);  // n_qtiles counts 256-row blocks here
+    const int b = bh / a.H;
+    const int h = bh - b * a.H;
+    const int q0 = qb * 2 * TILE;
+    const int n0 = kv_tiles_for(a, q0);
+    const int n1 = kv_tiles_for(a, q0 + TILE);
+    const int n = max(n0, n1);
 
     if (threadIdx.x == 0) {
         mbar_init(&sh.q_full, 1);
-        mbar_init(&sh.k_full, 1);
-        mbar_init(&sh.k_empty, 1);
-        mbar_init(&sh.v_full, 1);
-        mbar_init(&sh.v_empty, 1);
-        mbar_init(&sh.s_full, 1);
-        mbar_init(&sh.p_full, 128);
-        mbar_init(&sh.o_full, 1);
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(&sh.k_full[s], 1);
+            mbar_init(&sh.k_empty[s], 1);
+            mbar_init(&sh.v_full[s], 1);
+            mbar_init(&sh.v_empty[s], 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&sh.s_full[t], 1);
+            mbar_init(&sh.p_full[t], 128);
+            mbar_init(&sh.o_full[t], 1);
+        }
         sh.abort_flag = 0;
         fence_mbar_init();
     }
@@ -100,213 +132,278 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem = sh.tmem_base;
     WaitCtx wc{&sh.abort_flag, a.status};
+    const bool tl = a.timeline != nullptr && (int)blockIdx.x == a.timeline_block;
+    if (tl && threadIdx.x == 0) a.timeline[0] = n;
 
-    if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
-        if (lane == 0 && n_kv > 0) {
-            tma_prefetch_desc(&mapQ);
-            tma_prefetch_desc(&mapK);
-            tma_prefetch_desc(&mapV);
-            mbar_arrive_expect_tx(&sh.q_full, TILE_BYTES);
-            tma_load_4d(sQ, &mapQ, &sh.q_full, 0, q0, h, b);
-            tma_load_4d(sQ + BOX_BYTES, &mapQ, &sh.q_full, HALF_D, q0, h, b);
-            int issued = 0;  // key/value tiles whose loads were issued
-            for (int j = 0; j < n_kv; ++j) {
-                if (j > 0 && !mbar_wait(wc, &sh.k_empty, (j - 1) & 1, W_KEMPTY, j)) break;
-                mbar_arrive_expect_tx(&sh.k_full, TILE_BYTES);
-                tma_load_4d(sK, &mapK, &sh.k_full, 0, j * TILE, h, b);
-                tma_load_4d(sK + BOX_BYTES, &mapK, &sh.k_full, HALF_D, j * TILE, h, b);
-                if (j > 0 && !mbar_wait(wc, &sh.v_empty, (j - 1) & 1, W_VEMPTY, j)) {
-                    // K(j) is in flight: let it land before the CTA may exit
-                    for (int i = 0; i < 100000 && !mbar_try_wait(&sh.k_full, j & 1); ++i) {}
-                    break;
+    if (warp < 4) {
+        reg_release();
+        if (warp == 0) {
+            // ------------------------------ TMA producer ------------------------------
+            if (lane == 0 && n > 0) {
+                tma_prefetch_desc(&mapQ);
+                tma_prefetch_desc(&mapK);
+                tma_prefetch_desc(&mapV);
+                mbar_arrive_expect_tx(&sh.q_full, 2 * TILE_BYTES);
+                for (int t = 0; t < 2; ++t) {
+                    tma_load_4d(sQ + t * TILE_BYTES, &mapQ, &sh.q_full, 0, q0 + t * TILE, h, b);
+                    tma_load_4d(sQ + t * TILE_BYTES + BOX_BYTES, &mapQ, &sh.q_full, HALF_D, q0 + t * TILE, h, b);
                 }
-                mbar_arrive_expect_tx(&sh.v_full, TILE_BYTES);
-                tma_load_4d(sV, &mapV, &sh.v_full, 0, j * TILE, h, b);
-                tma_load_4d(sV + BOX_BYTES, &mapV, &sh.v_full, HALF_D, j * TILE, h, b);
-                issued = j + 1;
-            }
-            // Do not leave the CTA while bulk copies into its shared memory are in flight.
-            if (issued > 0) {
-                const uint32_t par = (issued - 1) & 1;
+                int issued = 0;
+                for (int j = 0; j < n; ++j) {
+                    const int s = j % NST;
+                    const uint32_t par = ((j / NST) - 1) & 1;
+                    if (j >= NST && !mbar_wait(wc, &sh.k_empty[s], par, W_KEMPTY, j)) break;
+                    mbar_arrive_expect_tx(&sh.k_full[s], TILE_BYTES);
+                    tma_load_4d(sK + s * TILE_BYTES, &mapK, &sh.k_full[s], 0, j * TILE, h, b);
+                    tma_load_4d(sK + s * TILE_BYTES + BOX_BYTES, &mapK, &sh.k_full[s], HALF_D, j * TILE, h, b);
+                    if (j >= NST && !mbar_wait(wc, &sh.v_empty[s], par, W_VEMPTY, j)) {
+                        for (int i = 0; i < 100000 && !mbar_try_wait(&sh.k_full[s], (j / NST) & 1); ++i) {}
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&sh.v_full[s], TILE_BYTES);
+                    tma_load_4d(sV + s * TILE_BYTES, &mapV, &sh.v_full[s], 0, j * TILE, h, b);
+                    tma_load_4d(sV + s * TILE_BYTES + BOX_BYTES, &mapV, &sh.v_full[s], HALF_D, j * TILE, h, b);
+                    issued = j + 1;
+                }
+                // Do not leave the CTA while bulk copies into its shared memory are in flight.
                 for (int i = 0; i < 100000 && !mbar_try_wait(&sh.q_full, 0); ++i) {}
-                for (int i = 0; i < 100000 && !mbar_try_wait(&sh.k_full, par); ++i) {}
-                for (int i = 0; i < 100000 && !mbar_try_wait(&sh.v_full, par); ++i) {}
+                for (int j = max(0, issued - NST); j < issued; ++j) {
+                    for (int i = 0; i < 100000 && !mbar_try_wait(&sh.k_full[j % NST], (j / NST) & 1); ++i) {}
+                    for (int i = 0; i < 100000 && !mbar_try_wait(&sh.v_full[j % NST], (j / NST) & 1); ++i) {}
+                }
+            }
+        } else if (warp == 1) {
+            // ------------------------------ MMA issuer ------------------------------
+            if (lane == 0 && n > 0) {
+                constexpr uint32_t IDESC_S = make_idesc_tf32(TILE, TILE, false, false);
+                constexpr uint32_t IDESC_O = make_idesc_tf32(TILE, HEAD_DIM, false, true);
+                const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+                auto issue_qk = [&](int t, int s) {
+#pragma unroll
+                    for (int kk = 0; kk < HEAD_DIM / 8; ++kk)
+                        umma_ss_tf32(tmem + COL_S0 + t * TILE, kmajor_desc(q_addr + t * TILE_BYTES, kk, BOX_BYTES),
+                                     kmajor_desc(k_addr + s * TILE_BYTES, kk, BOX_BYTES), IDESC_S, kk > 0);
+                    umma_commit(&sh.s_full[t]);
+                };
+                auto issue_pv = [&](int t, int s, bool first) {
+#pragma unroll
+                    for (int kk = 0; kk < TILE / 8; ++kk)
+                        umma_ts_tf32(tmem + COL_O0 + t * HEAD_DIM, tmem + COL_S0 + t * TILE + kk * 8,
+                                     mnmajor_desc(v_addr + s * TILE_BYTES, kk, BOX_BYTES), IDESC_O,
+                                     (!first || kk > 0) ? 1u : 0u);
+                    umma_commit(&sh.o_full[t]);
+                };
+                bool ok = mbar_wait(wc, &sh.q_full, 0, W_QFULL);
+                if (ok) ok = mbar_wait(wc, &sh.k_full[0], 0, W_KFULL, 0);
+                if (ok) {
+                    tc_fence_after_sync();
+                    if (0 < n0) issue_qk(0, 0);
+                    if (0 < n1) issue_qk(1, 0);
+                    umma_commit(&sh.k_empty[0]);
+                }
+                for (int j = 0; ok && j < n; ++j) {
+                    const int s = j % NST, s1 = (j + 1) % NST;
+                    const uint32_t par = (j / NST) & 1, par1 = ((j + 1) / NST) & 1;
+                    stamp(a, tl, j, 0, 0);
+                    if (!(ok = mbar_wait(wc, &sh.v_full[s], par, W_VFULL, j))) break;
+                    bool k_next_ready = false;
+                    for (int t = 0; t < 2; ++t) {
+                        const int nt = t == 0 ? n0 : n1;
+                        if (j < nt) {
+                            if (!(ok = mbar_wait(wc, &sh.p_full[t], j & 1, W_PFULL, j))) break;
+                            stamp(a, tl, j, 0, 1 + 3 * t);
+                            tc_fence_after_sync();
+                            issue_pv(t, s, j == 0);
+                            stamp(a, tl, j, 0, 2 + 3 * t);
+                        }
+                        if (t == 1) umma_commit(&sh.v_empty[s]);
+                        if (j + 1 < nt) {
+                            if (!k_next_ready) {
+                                if (!(ok = mbar_wait(wc, &sh.k_full[s1], par1, W_KFULL, j + 1))) break;
+                                tc_fence_after_sync();
+                                k_next_ready = true;
+                            }
+                            issue_qk(t, s1);
+                            stamp(a, tl, j, 0, 3 + 3 * t);
+                        }
+                    }
+                    if (!ok) break;
+                    if (j + 1 < n) umma_commit(&sh.k_empty[s1]);
+                }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0 && n_kv > 0) {
-            constexpr uint32_t IDESC_S = make_idesc_tf32(TILE, TILE, false, false);
-            constexpr uint32_t IDESC_O = make_idesc_tf32(TILE, HEAD_DIM, false, true);
-            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            bool ok = mbar_wait(wc, &sh.q_full, 0, W_QFULL);
-            for (int j = 0; ok && j < n_kv; ++j) {
-                const uint32_t par = j & 1;
-                if (!(ok = mbar_wait(wc, &sh.k_full, par, W_KFULL, j))) break;
-                tc_fence_after_sync();
-#pragma unroll
-                for (int kk = 0; kk < HEAD_DIM / 8; ++kk) {
-                    umma_ss_tf32(tmem + COL_S, kmajor_desc(q_addr, kk, BOX_BYTES), kmajor_desc(k_addr, kk, BOX_BYTES),
-                                 IDESC_S, kk > 0);
-                }
-                umma_commit(&sh.k_empty);
-                umma_commit(&sh.s_full);
-                if (!(ok = mbar_wait(wc, &sh.v_full, par, W_VFULL, j))) break;
-                if (!(ok = mbar_wait(wc, &sh.p_full, par, W_PFULL, j))) break;
-                tc_fence_after_sync();
-#pragma unroll
-                for (int kk = 0; kk < TILE / 8; ++kk) {
-                    umma_ts_tf32(tmem + COL_O, tmem + COL_S + kk * 8, mnmajor_desc(v_addr, kk, BOX_BYTES), IDESC_O,
-                                 (j > 0 || kk > 0) ? 1u : 0u);
-                }
-                umma_commit(&sh.v_empty);
-                umma_commit(&sh.o_full);
-            }
+        // teardown of the control warps (kept inside this branch: the two register regimes never
+        // share code after the hand-over)
+        tc_fence_before_sync();
+        __syncthreads();
+        if (warp == 1) {
+            __syncwarp();
+            tc_fence_after_sync();
+            tmem_dealloc(tmem, TMEM_COLS);
         }
     } else {
         // ------------------------------ softmax ------------------------------
+        reg_acquire();
+        const int t = (warp - 4) >> 2;                   // which of the two query tiles
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;             // row inside the query tile = tensor-memory lane
-        const int qrow = q0 + row;                       // row inside this (b,h)
+        const int qrow = q0 + t * TILE + row;            // row inside this (b,h)
         const bool row_ok = qrow < a.Tq;
+        const int nt = t == 0 ? n0 : n1;
         const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t tS = trow + COL_S0 + t * TILE;
+        const uint32_t tO = trow + COL_O0 + t * HEAD_DIM;
+        const bool tls = tl && row == 0;
         // last key index (local to this call's K) this row may see
         long long lim_ll = a.Tk - 1;
         if (a.causal) lim_ll = min(lim_ll, (long long)a.q_pos0 + qrow - a.k_pos0);
         const int kv_lim = row_ok ? (int)max(-1ll, lim_ll) : -1;
+        const float c = a.scale_log2e;
+        const float worst = (c >= 0.f) ? -INFINITY : INFINITY;  // raw score that can never win the max
 
-        float m = -INFINITY;  // running max, log2 units (score * scale * log2e)
+        float m = -INFINITY;  // running max actually used as exponent reference, log2 units
         float l = 0.f;
         bool ok = true;
-        uint32_t r[32];
+        uint32_t r[128];
 
-        for (int j = 0; j < n_kv; ++j) {
+        for (int j = 0; j < nt; ++j) {
+            stamp(a, tls, j, 1 + t, 0);
             // the vote keeps the warp converged for the .sync.aligned tensor-memory accesses below
-            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.s_full, j & 1, W_SFULL, j));
+            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.s_full[t], j & 1, W_SFULL, j));
             if (!ok) break;
+            stamp(a, tls, j, 1 + t, 1);
             tc_fence_after_sync();
+            tmem_ld32p(tS, r);
+            tmem_ld32p(tS + 32, r + 32);
+            tmem_ld32p(tS + 64, r + 64);
+            tmem_ld32p(tS + 96, r + 96);
             const int kv0 = j * TILE;
-            const bool full = (kv0 + TILE - 1 <= kv_lim);  // no masking needed for this row
-
-            // pass 1: row max of the scaled scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(trow + COL_S + c * 32, r);
-                tmem_wait_ld();
-                if (full) {
+            const int lim_local = kv_lim - kv0;  // columns 0..lim_local are visible
+            tmem_wait_ld();
+            stamp(a, tls, j, 1 + t, 2);
+            if (lim_local < TILE - 1) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]) * a.scale_log2e);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (kv0 + c * 32 + i <= kv_lim) mx = fmaxf(mx, __uint_as_float(r[i]) * a.scale_log2e);
-                }
+                for (int i = 0; i < 128; ++i)
+                    if (i > lim_local) r[i] = __float_as_uint(worst);
             }
-            const float m_new = fmaxf(m, mx);
-            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - m_use);
-
-            // rescale the running output (PV of the previous step has completed:
-            // s_full of this step was committed after it)
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+            // row max of the raw scores (min if the scale is negative), four chains
+            float mx0 = __uint_as_float(r[0]), mx1 = __uint_as_float(r[1]), mx2 = __uint_as_float(r[2]),
+                  mx3 = __uint_as_float(r[3]);
+            if (c >= 0.f) {
+#pragma unroll
+                for (int i = 4; i < 128; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+                }
+                mx0 = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            } else {
+#pragma unroll
+                for (int i = 4; i < 128; i += 4) {
+                    mx0 = fminf(mx0, __uint_as_float(r[i]));
+                    mx1 = fminf(mx1, __uint_as_float(r[i + 1]));
+                    mx2 = fminf(mx2, __uint_as_float(r[i + 2]));
+                    mx3 = fminf(mx3, __uint_as_float(r[i + 3]));
+                }
+                mx0 = fminf(fminf(mx0, mx1), fminf(mx2, mx3));
+            }
+            const float m_cand = mx0 * c;  // -inf when nothing is visible
+            // raise the reference only when it pays: a stale m makes p at most 2^8 larger, which fp32 absorbs
+            const bool raise = (m == -INFINITY) ? (m_cand > -INFINITY) : (m_cand > m + RESCALE_THRESHOLD);
+            const float m_new = raise ? m_cand : m;
+            const float alpha = raise ? ((m == -INFINITY) ? 0.f : ex2_approx(m - m_cand)) : 1.f;
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                // rescale the running output (PV of the previous step has completed: the commit that
+                // released S for this step was issued after it)
 #pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    tmem_ld32(trow + COL_O + c * 32, r);
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t o[32];
+                    tmem_ld32(tO + cc * 32, o);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_st32(trow + COL_O + c * 32, r);
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(tO + cc * 32, o);
                 }
             }
-
-            // pass 2: P = exp2(s*scale*log2e - m), masked, dropped, summed, rounded, written over S
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(trow + COL_S + c * 32, r);
-                tmem_wait_ld();
-                const int kc0 = kv0 + c * 32;
-                float e[32];
+            const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+            if (a.dropout_mode == 0) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = ex2_approx(fmaf(__uint_as_float(r[i]), a.scale_log2e, -m_use));
-                    if (!full && (kc0 + i > kv_lim)) v = 0.f;
-                    e[i] = v;
+                for (int i = 0; i < 128; i += 4) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), c, neg_m));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
+                    const float p2 = ex2_approx(fmaf(__uint_as_float(r[i + 2]), c, neg_m));
+                    const float p3 = ex2_approx(fmaf(__uint_as_float(r[i + 3]), c, neg_m));
+                    s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+                    r[i] = tf32_round_bits_mma(__float_as_uint(p0));
+                    r[i + 1] = tf32_round_bits_mma(__float_as_uint(p1));
+                    r[i + 2] = tf32_round_bits_mma(__float_as_uint(p2));
+                    r[i + 3] = tf32_round_bits_mma(__float_as_uint(p3));
                 }
-                if (a.dropout_mode == 2) {
-                    if (row_ok) {
+            } else if (a.dropout_mode == 2) {
 #pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            const uint32_t kpos = (uint32_t)(a.k_pos0 + kc0 + g * 4);
-                            hk_philox4_t w = hk_philox_row4(a.seed, a.offset, (uint32_t)bh,
-                                                            (uint32_t)(a.q_pos0 + qrow), kpos >> 2);
+                for (int g = 0; g < 32; ++g) {
+                    const uint32_t kpos = (uint32_t)(a.k_pos0 + kv0 + g * 4);
+                    hk_philox4_t w = hk_philox_row4(a.seed, a.offset, (uint32_t)bh, (uint32_t)(a.q_pos0 + qrow), kpos >> 2);
 #pragma unroll
-                            for (int t = 0; t < 4; ++t)
-                                if (w.v[t] < a.drop_thr) e[g * 4 + t] = 0.f;
-                        }
-                    }
-                } else if (a.dropout_mode == 1) {
-                    if (row_ok) {
-                        const float* mrow = a.mask + ((size_t)bh * a.Tq + qrow) * (size_t)a.Tk;
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (kc0 + i <= kv_lim) e[i] *= __ldg(mrow + kc0 + i);
+                    for (int u = 0; u < 4; ++u) {
+                        float p = ex2_approx(fmaf(__uint_as_float(r[g * 4 + u]), c, neg_m));
+                        if (w.v[u] < a.drop_thr) p = 0.f;
+                        s0 += p;
+                        r[g * 4 + u] = tf32_round_bits_mma(__float_as_uint(p));
                     }
                 }
+            } else {
+                const float* mrow = a.mask + ((size_t)bh * a.Tq + (row_ok ? qrow : 0)) * (size_t)a.Tk + kv0;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    sum += e[i];
-                    r[i] = tf32_round_bits(__float_as_uint(e[i]));
+                for (int i = 0; i < 128; ++i) {
+                    float p = ex2_approx(fmaf(__uint_as_float(r[i]), c, neg_m));
+                    p = (i <= lim_local) ? p * __ldg(mrow + i) : 0.f;
+                    s0 += p;
+                    r[i] = tf32_round_bits_mma(__float_as_uint(p));
                 }
-                tmem_st32(trow + COL_S + c * 32, r);
             }
-            l = l * alpha + sum;
+            tmem_st32p(tS, r);
+            tmem_st32p(tS + 32, r + 32);
+            tmem_st32p(tS + 64, r + 64);
+            tmem_st32p(tS + 96, r + 96);
+            l = l * alpha + ((s0 + s1) + (s2 + s3));
             m = m_new;
+            stamp(a, tls, j, 1 + t, 3);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&sh.p_full);
+            mbar_arrive(&sh.p_full[t]);
+            stamp(a, tls, j, 1 + t, 4);
         }
 
         // epilogue: O / l and LSE
-        if (ok && n_kv > 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.o_full, (n_kv - 1) & 1, W_OFULL, n_kv));
+        if (ok && nt > 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.o_full[t], (nt - 1) & 1, W_OFULL, nt));
         tc_fence_after_sync();
         const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-        float* orow = a.O + (int64_t)b * a.o_sB + (int64_t)h * a.o_sH + (int64_t)qrow * a.o_sM;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-            if (ok && n_kv > 0) {
-                tmem_ld32(trow + COL_O + c * 32, r);
-                tmem_wait_ld();
-            } else {
+        if (ok && nt > 0) {
+            tmem_ld32p(tO, r);
+            tmem_ld32p(tO + 32, r + 32);
+            tmem_wait_ld();
+        } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = 0u;
-            }
-            if (row_ok) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    float4 v;
-                    v.x = __uint_as_float(r[i]) * inv_l;
-                    v.y = __uint_as_float(r[i + 1]) * inv_l;
-                    v.z = __uint_as_float(r[i + 2]) * inv_l;
-                    v.w = __uint_as_float(r[i + 3]) * inv_l;
-                    *reinterpret_cast<float4*>(orow + c * 32 + i) = v;
-                }
-            }
+            for (int i = 0; i < 64; ++i) r[i] = 0u;
         }
-        if (row_ok)
-            a.LSE[(int64_t)b * a.lse_sB + (int64_t)h * a.lse_sH + qrow] =
-                (l > 0.f) ? (m + log2f(l)) * LN2 : -INFINITY;
-    }
-
-    // ------------------------------ teardown ------------------------------
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 1) {
-        __syncwarp();
-        tc_fence_after_sync();
-        tmem_dealloc(tmem, TMEM_COLS);
+        if (row_ok) {
+            float* orow = a.O + (int64_t)b * a.o_sB + (int64_t)h * a.o_sH + (int64_t)qrow * a.o_sM;
+#pragma unroll
+            for (int i = 0; i < 64; i += 4) {
+                float4 v;
+                v.x = __uint_as_float(r[i]) * inv_l;
+                v.y = __uint_as_float(r[i + 1]) * inv_l;
+                v.z = __uint_as_float(r[i + 2]) * inv_l;
+                v.w = __uint_as_float(r[i + 3]) * inv_l;
+                *reinterpret_cast<float4*>(orow + i) = v;
+            }
+            a.LSE[(int64_t)b * a.lse_sB + (int64_t)h * a.lse_sH + qrow] = (l > 0.f) ? (m + log2f(l)) * LN2 : -INFINITY;
+        }
+        tc_fence_before_sync();
+        __syncthreads();  // pairs with the control warps' barrier before tensor memory is freed
     }
 }
 

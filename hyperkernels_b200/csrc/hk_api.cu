@@ -245,7 +245,7 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
         if (!stride_ok(s)) return HK_ERR_MISALIGNED;
     if (p->q_strideM < HEAD_DIM || p->k_strideM < HEAD_DIM || p->v_strideM < HEAD_DIM || p->o_strideM < HEAD_DIM)
         return HK_ERR_BAD_SHAPE;
-    if (!std::isfinite(p->scale)) return HK_ERR_BAD_SHAPE;
+    if (!std::isfinite(p->scale) || p->scale == 0.f) return HK_ERR_BAD_SHAPE;  // masking multiplies -inf by the scale
     int mode = 0;
     int rc = validate_dropout(p->dropout_p, p->dropout_mask, p->flags, p->k_pos0, &mode);
     if (rc != HK_OK) return rc;
@@ -283,7 +283,7 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     a.o_sB = p->o_strideB; a.o_sM = p->o_strideM; a.o_sH = p->o_strideH;
     a.lse_sB = p->lse_strideB; a.lse_sH = p->lse_strideH;
     a.H = H; a.BH = BH; a.Tq = (int)Tq; a.Tk = (int)Tk;
-    a.n_qtiles = (int)((Tq + TILE - 1) / TILE);
+    a.n_qtiles = (int)((Tq + 2 * TILE - 1) / (2 * TILE));  // the forward takes two 128-row tiles per CTA
     a.q_pos0 = (int)p->q_pos0; a.k_pos0 = (int)p->k_pos0;
     a.scale_log2e = p->scale * LOG2E;
     a.causal = p->is_causal ? 1 : 0;

@@ -96,7 +96,7 @@ struct WaitCtx {
     DeviceStatus* status;      // global memory
 };
 
-static __device__ __noinline__ bool mbar_wait_slow(const WaitCtx& ctx, uint64_t* bar, uint32_t parity, int wait_id, int aux) {
+static __device__ __forceinline__ bool mbar_wait_slow(const WaitCtx& ctx, uint64_t* bar, uint32_t parity, int wait_id, int aux) {
     const unsigned long long t0 = globaltimer_ns();
     while (true) {
         for (int i = 0; i < 64; ++i)
