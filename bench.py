@@ -332,6 +332,122 @@ def run_ours(args, cfg, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def run_ours_ring(args, cfg, rank, local_rank, world):
+    """Config 5 on N > 1 GPUs: heads split over N / ring groups, the sequence of each group sharded over `ring`
+    ranks with the KV ring of hyperkernels_b200/ring.py (NCCL send/recv overlapped with compute).  Strong scaling:
+    the problem is the one config-5 problem whatever N is."""
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+
+    import hyperkernels_b200 as hk
+    from hyperkernels_b200.ring import RingAttention, segments_of
+
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = hk.lib()
+    Gs = args.ring
+    assert world % Gs == 0 and cfg["H"] % (world // Gs) == 0
+    Gh = world // Gs
+    groups = [dist.new_group(list(range(g * Gs, (g + 1) * Gs))) for g in range(Gh)]
+    group = groups[rank // Gs]
+    srank = rank % Gs
+    Hl, N = cfg["H"] // Gh, cfg["N"]
+    segs = segments_of(srank, Gs, N, "zigzag")
+    gen = torch.Generator(device="cuda").manual_seed(2000 + rank)
+    shape = (cfg["B"], Hl, N // Gs, 64)
+    Q, K, V, dO = (torch.randn(shape, generator=gen, device="cuda") for _ in range(4))
+    off = 0
+    for (s0, n) in segs:  # every 64th key of the GLOBAL sequence scaled x8
+        first = (-s0) % 64
+        K[:, :, off + first:off + n:64] *= 8.0
+        off += n
+    ring = RingAttention(N, 0.125, True, group=group, layout="zigzag")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream()
+    out = {}
+
+    def step():
+        out["O"], out["LSE"] = ring.forward(Q, K, V)
+        out["dQ"], out["dK"], out["dV"] = ring.backward(Q, K, V, out["O"], out["LSE"], dO)
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    assert hk.last_device_status() == 0
+    clocks = ClockSampler(local_rank)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    L.hk_attn_kernel_timing_enable(1)
+    n0 = hk.launch_count()
+    barrier()
+    clocks.start()
+    for a, b in ev:
+        flush.zero_()
+        a.record(stream)
+        step()
+        b.record(stream)
+    barrier()
+    launches = hk.launch_count() - n0
+    L.hk_attn_kernel_timing_enable(0)
+    ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
+    kt = {}
+    for kind, name in ((0, "fwd"), (1, "bwd")):
+        tot, n = C.c_double(), C.c_int()
+        L.hk_attn_kernel_timing_read(kind, C.byref(tot), C.byref(n))
+        kt[name] = tot.value / args.steps  # all kernel launches of that kind in one step, summed
+    hQ, hK, hV, hdO = (t.cpu().pin_memory() for t in (Q, K, V, dO))
+    hout = {k: torch.empty(v.shape).pin_memory() for k, v in out.items()}
+
+    def e2e_step():
+        Q.copy_(hQ, non_blocking=True); K.copy_(hK, non_blocking=True)
+        V.copy_(hV, non_blocking=True); dO.copy_(hdO, non_blocking=True)
+        step()
+        for k in hout:
+            hout[k].copy_(out[k], non_blocking=True)
+
+    e2e_step()
+    barrier()
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in ev2:
+        a.record(stream)
+        e2e_step()
+        b.record(stream)
+    barrier()
+    ms_e2e = sum(a.elapsed_time(b) for a, b in ev2) / args.steps
+    clk = clocks.stop()
+    t = torch.tensor([ms, ms_e2e, kt["fwd"], kt["bwd"]], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e, kt["fwd"], kt["bwd"] = (float(x) for x in t.tolist())
+    if rank == 0:
+        peaks = measured_peaks()
+        total = flops(cfg)
+        achieved = flops(cfg, fwd=False) / world / (kt["bwd"] * 1e-3) / 1e12 if kt["bwd"] > 0 else None
+        print(json.dumps({
+            "metric": METRIC, "value": total / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+            "config": {"workload": cfg["name"], "config_id": args.config, "mesh": f"{Gh} head groups x {Gs}-rank KV ring (zigzag)",
+                       "l2": "256 MiB buffer written between timed steps (untimed)",
+                       "step": "ring forward + ring backward (hk_attn_forward/backward per segment pair, NCCL send/recv)"},
+            "pct_of_tf32_peak": total / world / (ms * 1e-3) / 1e12 / peaks["tf32_tflops"],
+            "kernel_ms": {"fwd_kernels_per_step": kt["fwd"], "bwd_kernels_per_step": kt["bwd"]},
+            "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel", "achieved": achieved, "peak": peaks["tf32_tflops"],
+                         "unit": "TFLOP/s", "frac": (achieved / peaks["tf32_tflops"]) if achieved else None,
+                         "peak_source": peaks["source"], "traffic": None},
+            "e2e": {"value": total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 4 * Q.numel() * 4,
+                    "d2h_bytes_per_step": sum(v.numel() for v in out.values()) * 4, "ms_per_step": ms_e2e},
+            "gpu_launches": int(launches), "clocks": clk,
+        }))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -340,6 +456,7 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ring", type=int, default=2, help="config 5 on N > 1 GPUs: ranks per sequence ring")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -347,6 +464,8 @@ def main():
     cfg = CONFIGS[args.config]
     if args.impl == "reference":
         run_reference(args, cfg, rank, world)
+    elif args.config == 5 and world > 1:
+        run_ours_ring(args, cfg, rank, local_rank, world)
     else:
         run_ours(args, cfg, rank, local_rank, world)
 

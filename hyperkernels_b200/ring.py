@@ -1,0 +1,210 @@
+"""Sequence-sharded attention over a ring of ranks (the long-sequence config).
+
+The reference has no multi-GPU path at all; this module is the host-side schedule
+that shards ONE attention problem over the sequence: every rank keeps its slice
+of Q (and of O, LSE, dO, dQ) and the K/V slices travel round the ring with
+``torch.distributed`` send/recv (NCCL over NVLink on GPUs), one hop per step,
+overlapped with the compute of the step.  The compute of a step is a plain call
+of the single-GPU kernels through the C ABI on a (query segment, key segment)
+pair, told where the two segments sit in the global sequence
+(``q_pos0``/``k_pos0``); partial forward results are merged with
+``hk_attn_merge_partial``; in the backward each rank computes its contribution to
+the gradient of the visiting K/V block and adds it to an accumulator that
+travels one step behind the block.
+
+Layouts: ``contiguous`` (rank r owns positions [r*T/G, (r+1)*T/G)) or ``zigzag``
+(the sequence is cut in 2G chunks and rank r owns chunks r and 2G-1-r, which
+balances the causal mask).  Fully masked (segment, segment) pairs are skipped.
+
+The kernels are reached through a small backend object so that the schedule can
+be exercised on CPU ranks (gloo) with a stand-in backend in the tests; the
+product backend is ``CudaBackend`` and needs the compiled library and a GPU.
+"""
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def segments_of(rank: int, world: int, T: int, layout: str) -> List[Tuple[int, int]]:
+    """(global start, length) of the sequence segments rank `rank` owns, in local storage order."""
+    if layout == "contiguous":
+        assert T % world == 0
+        c = T // world
+        return [(rank * c, c)]
+    if layout == "zigzag":
+        assert T % (2 * world) == 0
+        c = T // (2 * world)
+        return [(rank * c, c), ((2 * world - 1 - rank) * c, c)]
+    raise ValueError(layout)
+
+
+def visible(qseg, kseg, causal: bool) -> bool:
+    """False when the causal mask hides every key of kseg from every query of qseg."""
+    return (not causal) or kseg[0] <= qseg[0] + qseg[1] - 1
+
+
+class CudaBackend:
+    """The sm_100a kernels through the C ABI (hyperkernels_b200.attention)."""
+
+    def __init__(self):
+        from . import attention as att
+
+        self.att = att
+
+    def fwd(self, Q, K, V, scale, causal, q_pos0, k_pos0):
+        return self.att.attention_forward(Q, K, V, scale, causal, q_pos0=q_pos0, k_pos0=k_pos0)
+
+    def merge(self, O_acc, LSE_acc, O_part, LSE_part):
+        self.att.merge_partial(O_acc, LSE_acc, O_part, LSE_part)
+
+    def precompute_D(self, dO, O):
+        import ctypes as C
+
+        B, H, T, _ = dO.shape
+        D = torch.empty((B, H, T), dtype=torch.float32, device=dO.device)
+        p = self.att.MemEfficientBwdParams()
+        p.dO, p.O, p.D = dO.data_ptr(), O.data_ptr(), D.data_ptr()
+        p.B, p.nh, p.T, p.scale = B, H, T, 1.0
+        p.do_strideB, p.do_strideM, p.do_strideH = dO.stride(0), dO.stride(2), dO.stride(1)
+        p.o_strideB, p.o_strideM, p.o_strideH = O.stride(0), O.stride(2), O.stride(1)
+        p.d_strideB, p.d_strideH = D.stride(0), D.stride(1)
+        self.att.mem_efficient_bwd_precompute_D(p)
+        return D
+
+    def bwd(self, Q, K, V, O, dO, LSE, D, scale, causal, q_pos0, k_pos0, dQ):
+        """Adds this pair's contribution into dQ (in place); returns the pair's (dK, dV).
+        D = rowsum(dO * O) of the FINAL output is passed in, so O itself is not needed here."""
+        _, dK, dV, _ = self.att.attention_backward(Q, K, V, None, dO, LSE, scale, causal, q_pos0=q_pos0, k_pos0=k_pos0,
+                                                   D=D, d_precomputed=True, accum_dq=True, dQ=dQ)
+        return dK, dV
+
+
+class RingAttention:
+    """Attention of a sequence of length T sharded over the ranks of `group`.
+
+    All tensors are this rank's shards, [B, H, T/G, 64] fp32 (LSE: [B, H, T/G]), stored in the order of
+    ``segments_of(rank, G, T, layout)``.
+    """
+
+    def __init__(self, T: int, scale: float, causal: bool, group=None, layout: str = "zigzag", backend=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.T, self.scale, self.causal, self.layout = T, scale, causal, layout
+        self.backend = backend if backend is not None else CudaBackend()
+        self.my_segs = segments_of(self.rank, self.world, T, layout)
+        self.comm_stream = torch.cuda.Stream() if torch.cuda.is_available() and backend is None else None
+
+    # ---- plumbing ---------------------------------------------------------------
+    def _peer(self, offset: int) -> int:
+        r = (self.rank + offset) % self.world
+        return dist.get_global_rank(self.group, r) if self.group is not None else r
+
+    def _exchange(self, send_buf, recv_buf):
+        """Post send to the next rank and receive from the previous one; returns the requests."""
+        ops = [dist.P2POp(dist.isend, send_buf, self._peer(+1), self.group),
+               dist.P2POp(dist.irecv, recv_buf, self._peer(-1), self.group)]
+        return dist.batch_isend_irecv(ops)
+
+    def _start_exchange(self, send_buf, recv_buf):
+        if self.comm_stream is None:
+            return self._exchange(send_buf, recv_buf), None
+        # the communication stream must see the data the compute stream produced
+        self.comm_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.comm_stream):
+            reqs = self._exchange(send_buf, recv_buf)
+        return reqs, self.comm_stream
+
+    @staticmethod
+    def _finish(handle):
+        reqs, stream = handle
+        for r in reqs:
+            r.wait()
+        if stream is not None:
+            torch.cuda.current_stream().wait_stream(stream)
+
+    def _seg_views(self, x, segs):
+        """Views of x ([B,H,Tl,...]) per segment, in storage order."""
+        out, off = [], 0
+        for (_, n) in segs:
+            out.append(x[:, :, off:off + n])
+            off += n
+        return out
+
+    # ---- forward ------------------------------------------------------------------
+    def forward(self, Q, K, V):
+        G = self.world
+        q_views = self._seg_views(Q, self.my_segs)
+        O_acc = [torch.zeros(v.shape, dtype=torch.float32, device=Q.device) for v in q_views]
+        LSE_acc = [torch.full(v.shape[:3], float("-inf"), dtype=torch.float32, device=Q.device) for v in q_views]
+        kv = torch.stack([K, V]).contiguous()  # one message per hop
+        for t in range(G):
+            src = (self.rank - t) % G
+            handle = None
+            if t + 1 < G:
+                nxt = torch.empty_like(kv)
+                handle = self._start_exchange(kv, nxt)  # overlaps with the compute below
+            k_views = self._seg_views(kv[0], segments_of(src, G, self.T, self.layout))
+            v_views = self._seg_views(kv[1], segments_of(src, G, self.T, self.layout))
+            for qi, qseg in enumerate(self.my_segs):
+                for ki, kseg in enumerate(segments_of(src, G, self.T, self.layout)):
+                    if not visible(qseg, kseg, self.causal):
+                        continue
+                    O_p, L_p = self.backend.fwd(q_views[qi], k_views[ki], v_views[ki], self.scale, self.causal,
+                                                qseg[0], kseg[0])
+                    self.backend.merge(O_acc[qi], LSE_acc[qi], O_p.contiguous(), L_p.contiguous())
+            if handle is not None:
+                self._finish(handle)
+                kv = nxt
+        return torch.cat(O_acc, dim=2), torch.cat(LSE_acc, dim=2)
+
+    # ---- backward -----------------------------------------------------------------
+    def backward(self, Q, K, V, O, LSE, dO):
+        G = self.world
+        D = self.backend.precompute_D(dO.contiguous(), O.contiguous())
+        q_views = self._seg_views(Q, self.my_segs)
+        do_views = self._seg_views(dO, self.my_segs)
+        o_views = self._seg_views(O, self.my_segs)
+        lse_views = [v.contiguous() for v in self._seg_views(LSE, self.my_segs)]
+        d_views = [v.contiguous() for v in self._seg_views(D, self.my_segs)]
+        dQ = torch.zeros_like(Q)
+        dq_views = self._seg_views(dQ, self.my_segs)
+        kv = torch.stack([K, V]).contiguous()
+        acc = None  # gradient accumulator of the block processed in the previous step, on its way to the next rank
+        acc_handle = None
+        for t in range(G):
+            src = (self.rank - t) % G
+            src_segs = segments_of(src, G, self.T, self.layout)
+            kv_handle = None
+            if t + 1 < G:
+                nxt = torch.empty_like(kv)
+                kv_handle = self._start_exchange(kv, nxt)
+            k_views = self._seg_views(kv[0], src_segs)
+            v_views = self._seg_views(kv[1], src_segs)
+            part = torch.zeros_like(kv)  # this rank's (dK, dV) contribution to the visiting block
+            pk_views = self._seg_views(part[0], src_segs)
+            pv_views = self._seg_views(part[1], src_segs)
+            for qi, qseg in enumerate(self.my_segs):
+                for ki, kseg in enumerate(src_segs):
+                    if not visible(qseg, kseg, self.causal):
+                        continue
+                    dK_p, dV_p = self.backend.bwd(q_views[qi], k_views[ki], v_views[ki], o_views[qi], do_views[qi],
+                                                  lse_views[qi], d_views[qi], self.scale, self.causal, qseg[0], kseg[0],
+                                                  dq_views[qi])
+                    pk_views[ki].add_(dK_p)
+                    pv_views[ki].add_(dV_p)
+            # the accumulator of this block left the previous rank one step ago
+            if t > 0:
+                self._finish(acc_handle)
+                part.add_(acc_in)
+            if kv_handle is not None:
+                self._finish(kv_handle)
+                kv = nxt
+            acc = part
+            acc_in = torch.empty_like(acc)
+            acc_handle = self._start_exchange(acc, acc_in)  # t < G-1: to the next worker; t = G-1: the hop home
+        self._finish(acc_handle)
+        return dQ, acc_in[0], acc_in[1]
