@@ -23,10 +23,14 @@
 // Q, dO and K each feed one product that contracts over d (K-major operand,
 // 16-byte-chunk swizzle) and one that contracts over the sequence (MN-major
 // operand, which for TF32 must use the 32-byte-chunk swizzle), so TMA brings
-// each of them into shared memory twice, once per swizzle.  The K-major copies
-// of Q and dO are dead once S^T and dP^T are done, and dS is staged over them.
-// The MN-major copies are released as soon as dV and dK have consumed them, so
-// their reload overlaps dQ = dS K and its drain.
+// each of them into shared memory twice, once per swizzle.  The MN-major copies
+// of Q and dO are dead once dV and dK have consumed them, and dS is staged over
+// them for dQ = dS K; the K-major copies are free as soon as S^T and dP^T are
+// done, so the next query tile's are prefetched a whole tile ahead.
+//
+// Tensor-pipe order per query tile i:  dV(i), dK(i) | S^T(i+1), dP^T(i+1) | dQ(i).
+// The compute warps work on tile i+1 while dQ(i) executes, and write dS(i) to
+// shared memory while S^T(i+1), dP^T(i+1) execute.
 //
 //   warp 0     TMA producer (K, V once; Q and dO per query tile)
 //   warp 1     MMA issuer
@@ -52,7 +56,7 @@ constexpr int COL_DQ = 384;
 struct __align__(16) Shared {
     float lse[2][TILE];   // LSE * log2e of the query tile (+inf for rows past the end), double-buffered
     float dsum[2][TILE];  // D * scale of the query tile
-    uint64_t kv_full, qk_full, qk_empty, qm_full, qm_empty, s_full, ds_ready, dq_full, dq_empty, staged;
+    uint64_t kv_full, qk_full, qk_empty, qm_full, qm_free, s_full, p_ready, b_done, ds_ready, dq_full, dq_empty, staged;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -60,11 +64,11 @@ struct __align__(16) Shared {
 constexpr int OFF_KK = 0;                // K, K-major swizzle   (S^T = K Q^T)
 constexpr int OFF_KM = TILE_BYTES;       // K, MN-major swizzle  (dQ = dS K)
 constexpr int OFF_V = 2 * TILE_BYTES;    // V, K-major           (dP^T = V dO^T)
-constexpr int OFF_QK = 3 * TILE_BYTES;   // Q, K-major           (S^T)      } dS staging, 4 boxes of
-constexpr int OFF_DOK = 4 * TILE_BYTES;  // dO, K-major          (dP^T)     } [128 kv][32 q], overlays these two
-constexpr int OFF_DS = OFF_QK;
-constexpr int OFF_QM = 5 * TILE_BYTES;   // Q, MN-major          (dK += dS^T Q)
-constexpr int OFF_DOM = 6 * TILE_BYTES;  // dO, MN-major         (dV += P^T dO)
+constexpr int OFF_QK = 3 * TILE_BYTES;   // Q, K-major           (S^T)
+constexpr int OFF_DOK = 4 * TILE_BYTES;  // dO, K-major          (dP^T)
+constexpr int OFF_QM = 5 * TILE_BYTES;   // Q, MN-major          (dK += dS^T Q)   } dS staging, 4 boxes of
+constexpr int OFF_DOM = 6 * TILE_BYTES;  // dO, MN-major         (dV += P^T dO)   } [128 kv][32 q], overlays these two
+constexpr int OFF_DS = OFF_QM;
 constexpr int OFF_SH = 7 * TILE_BYTES;
 // no slack for re-aligning the dynamic shared-memory base: it is declared 1024-byte aligned
 // and the kernel checks that it is (the 128-byte swizzles need it)
@@ -78,7 +82,8 @@ __device__ __forceinline__ void stamp(const BwdArgs& a, bool on, int it, int rol
 }
 
 enum WaitId {
-    W_KVFULL = 201, W_QKFULL, W_QKEMPTY, W_QMFULL, W_QMEMPTY, W_SFULL, W_DSREADY, W_DQFULL, W_DQEMPTY, W_STAGED
+    W_KVFULL = 201, W_QKFULL, W_QKEMPTY, W_QMFULL, W_QMFREE, W_SFULL, W_PREADY, W_BDONE, W_DSREADY, W_DQFULL, W_DQEMPTY,
+    W_STAGED
 };
 
 }  // namespace bwd
@@ -128,8 +133,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         mbar_init(&sh.qk_full, 1);
         mbar_init(&sh.qk_empty, 1);
         mbar_init(&sh.qm_full, 1);
-        mbar_init(&sh.qm_empty, 1);
+        mbar_init(&sh.qm_free, 1);
         mbar_init(&sh.s_full, 1);
+        mbar_init(&sh.p_ready, NUM_COMPUTE);
+        mbar_init(&sh.b_done, 1);
         mbar_init(&sh.ds_ready, NUM_COMPUTE);
         mbar_init(&sh.dq_full, 1);
         mbar_init(&sh.dq_empty, 256);  // the two column groups that drain dQ
@@ -167,36 +174,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tma_load_4d(sKm, &mapKm, &sh.kv_full, 0, kv0, h, b);
             tma_load_4d(sKm + BOX_BYTES, &mapKm, &sh.kv_full, HALF_D, kv0, h, b);
             int issued_k = 0, issued_m = 0;
-            for (int it = 0; it < n_it; ++it) {
-                const int q0 = (it0 + it) * TILE;
-                // K-major Q, dO (also the dS staging area: free once dQ of the previous tile is done)
-                if (it > 0 && !mbar_wait(wc, &sh.qk_empty, (it - 1) & 1, W_QKEMPTY, it)) break;
+            auto load_qk = [&](int q0) {
                 mbar_arrive_expect_tx(&sh.qk_full, 2 * TILE_BYTES);
                 tma_load_4d(sQ, &mapQ, &sh.qk_full, 0, q0, h, b);
                 tma_load_4d(sQ + BOX_BYTES, &mapQ, &sh.qk_full, HALF_D, q0, h, b);
                 tma_load_4d(sdO, &mapdO, &sh.qk_full, 0, q0, h, b);
                 tma_load_4d(sdO + BOX_BYTES, &mapdO, &sh.qk_full, HALF_D, q0, h, b);
-                issued_k = it + 1;
-                // MN-major Q, dO of the NEXT tile are requested below, ahead of time; the first tile's here
-                if (it == 0) {
-                    mbar_arrive_expect_tx(&sh.qm_full, 2 * TILE_BYTES);
-                    tma_load_4d(sQm, &mapQm, &sh.qm_full, 0, q0, h, b);
-                    tma_load_4d(sQm + BOX_BYTES, &mapQm, &sh.qm_full, HALF_D, q0, h, b);
-                    tma_load_4d(sdOm, &mapdOm, &sh.qm_full, 0, q0, h, b);
-                    tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qm_full, HALF_D, q0, h, b);
-                    issued_m = 1;
-                }
-                if (it + 1 < n_it) {
-                    // released right after dV/dK of tile `it`: reload overlaps dQ = dS K and its drain
-                    if (!mbar_wait(wc, &sh.qm_empty, it & 1, W_QMEMPTY, it)) break;
-                    const int q1 = q0 + TILE;
-                    mbar_arrive_expect_tx(&sh.qm_full, 2 * TILE_BYTES);
-                    tma_load_4d(sQm, &mapQm, &sh.qm_full, 0, q1, h, b);
-                    tma_load_4d(sQm + BOX_BYTES, &mapQm, &sh.qm_full, HALF_D, q1, h, b);
-                    tma_load_4d(sdOm, &mapdOm, &sh.qm_full, 0, q1, h, b);
-                    tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qm_full, HALF_D, q1, h, b);
-                    issued_m = it + 2;
-                }
+                ++issued_k;
+            };
+            auto load_qm = [&](int q0) {
+                mbar_arrive_expect_tx(&sh.qm_full, 2 * TILE_BYTES);
+                tma_load_4d(sQm, &mapQm, &sh.qm_full, 0, q0, h, b);
+                tma_load_4d(sQm + BOX_BYTES, &mapQm, &sh.qm_full, HALF_D, q0, h, b);
+                tma_load_4d(sdOm, &mapdOm, &sh.qm_full, 0, q0, h, b);
+                tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qm_full, HALF_D, q0, h, b);
+                ++issued_m;
+            };
+            load_qk(it0 * TILE);
+            load_qm(it0 * TILE);
+            for (int it = 0; it + 1 < n_it; ++it) {
+                const int q1 = (it0 + it + 1) * TILE;
+                // K-major Q, dO: free as soon as S^T(it), dP^T(it) are done
+                if (!mbar_wait(wc, &sh.qk_empty, it & 1, W_QKEMPTY, it)) break;
+                load_qk(q1);
+                // MN-major Q, dO double as the dS staging area: free once dQ(it) is done
+                if (!mbar_wait(wc, &sh.qm_free, it & 1, W_QMFREE, it)) break;
+                load_qm(q1);
             }
             // Do not leave the CTA while bulk copies into its shared memory are in flight.
             for (int i = 0; i < 100000 && !mbar_try_wait(&sh.kv_full, 0); ++i) {}
@@ -214,13 +217,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             const uint32_t k_addr = smem_u32(sK), km_addr = smem_u32(sKm), v_addr = smem_u32(sV), q_addr = smem_u32(sQ),
                            do_addr = smem_u32(sdO), qm_addr = smem_u32(sQm), dom_addr = smem_u32(sdOm),
                            ds_addr = smem_u32(sdS);
-            bool ok = mbar_wait(wc, &sh.kv_full, 0, W_KVFULL);
-            for (int it = 0; ok && it < n_it; ++it) {
-                const uint32_t par = it & 1;
-                stamp(a, tl, it, 0, 0);
-                if (!(ok = mbar_wait(wc, &sh.qk_full, par, W_QKFULL, it))) break;
-                stamp(a, tl, it, 0, 1);
-                tc_fence_after_sync();
+            auto issue_a = [&]() {
 #pragma unroll
                 for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // S^T = K Q^T
                     umma_ss_tf32(tmem + COL_S, kmajor_desc(k_addr, kk, BOX_BYTES), kmajor_desc(q_addr, kk, BOX_BYTES),
@@ -230,11 +227,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     umma_ss_tf32(tmem + COL_DP, kmajor_desc(v_addr, kk, BOX_BYTES), kmajor_desc(do_addr, kk, BOX_BYTES),
                                  IDESC_ST, kk > 0);
                 umma_commit(&sh.s_full);
-                stamp(a, tl, it, 0, 2);
+                umma_commit(&sh.qk_empty);
+            };
+            bool ok = mbar_wait(wc, &sh.kv_full, 0, W_KVFULL);
+            if (ok) ok = mbar_wait(wc, &sh.qk_full, 0, W_QKFULL, 0);
+            if (ok) {
+                tc_fence_after_sync();
+                issue_a();
+            }
+            for (int it = 0; ok && it < n_it; ++it) {
+                const uint32_t par = it & 1;
+                stamp(a, tl, it, 0, 0);
                 if (!(ok = mbar_wait(wc, &sh.qm_full, par, W_QMFULL, it))) break;
-                stamp(a, tl, it, 0, 3);
-                if (!(ok = mbar_wait(wc, &sh.ds_ready, par, W_DSREADY, it))) break;
-                stamp(a, tl, it, 0, 4);
+                if (!(ok = mbar_wait(wc, &sh.p_ready, par, W_PREADY, it))) break;
+                stamp(a, tl, it, 0, 1);
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < TILE / 8; ++kk)  // dV += P^T dO
@@ -244,7 +250,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 for (int kk = 0; kk < TILE / 8; ++kk)  // dK += dS^T Q
                     umma_ts_tf32(tmem + COL_DK, tmem + COL_DP + kk * 8, mnmajor_desc(qm_addr, kk, BOX_BYTES), IDESC_TS,
                                  (it > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&sh.qm_empty);
+                umma_commit(&sh.b_done);  // MN-major Q, dO consumed: the compute warps may stage dS over them
+                stamp(a, tl, it, 0, 2);
+                if (it + 1 < n_it) {
+                    // next tile's S^T, dP^T: P^T and dS^T of this tile were consumed by the MMAs just issued
+                    if (!(ok = mbar_wait(wc, &sh.qk_full, (it + 1) & 1, W_QKFULL, it + 1))) break;
+                    stamp(a, tl, it, 0, 3);
+                    tc_fence_after_sync();
+                    issue_a();
+                    stamp(a, tl, it, 0, 4);
+                }
+                if (!(ok = mbar_wait(wc, &sh.ds_ready, par, W_DSREADY, it))) break;
                 stamp(a, tl, it, 0, 5);
                 if (it > 0 && !(ok = mbar_wait(wc, &sh.dq_empty, (it - 1) & 1, W_DQEMPTY, it))) break;
                 stamp(a, tl, it, 0, 6);
@@ -253,7 +269,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 for (int kk = 0; kk < TILE / 8; ++kk)  // dQ = dS K
                     umma_ss_tf32(tmem + COL_DQ, mnmajor_desc(ds_addr, kk, BOX_BYTES), mnmajor_desc(km_addr, kk, BOX_BYTES),
                                  IDESC_DQ, kk > 0);
-                umma_commit(&sh.qk_empty);
+                umma_commit(&sh.qm_free);
                 umma_commit(&sh.dq_full);
                 stamp(a, tl, it, 0, 7);
             }
@@ -387,33 +403,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     }
                 }
             }
+            stamp(a, tlc, it, 1, 4);
             tmem_st32(trow + COL_S + c0, rs);
             tmem_st32(trow + COL_DP + c0, rp);
-            // dS into shared memory (MN-major A operand of dQ = dS K): box `part` holds query
-            // columns 32*part..32*part+31, one 128-byte row per key row, 32-byte chunks
-            // XOR-swizzled with (row & 3)
-            {
-                uint8_t* drow = sdS + part * BOX_BYTES + row * 128;
-#pragma unroll
-                for (int t = 0; t < 8; ++t) {
-                    uint4 v = make_uint4(rp[4 * t], rp[4 * t + 1], rp[4 * t + 2], rp[4 * t + 3]);
-                    *reinterpret_cast<uint4*>(drow + ((((t >> 1) ^ (row & 3)) << 5) | ((t & 1) << 4))) = v;
-                }
-            }
-            stamp(a, tlc, it, 1, 4);
             tmem_wait_st();
-            fence_proxy_async_smem();
             tc_fence_before_sync();
-            mbar_arrive(&sh.ds_ready);
+            mbar_arrive(&sh.p_ready);  // dV += P^T dO and dK += dS^T Q may go
             stamp(a, tlc, it, 1, 5);
 
-            // drain dQ of this query tile (lane = query row): column groups 0 and 1 take 32 columns each
-            if (part < 2) {
-                ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, it & 1, W_DQFULL, it));
+            // drain dQ of the PREVIOUS query tile (lane = query row; column groups 0 and 1 take 32 columns
+            // each): its dQ = dS K was issued behind this tile's S^T, dP^T and has had this tile's compute to finish
+            if (it > 0 && part < 2) {
+                ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (it - 1) & 1, W_DQFULL, it - 1));
                 if (!ok) break;
-                stamp(a, tlc, it, 1, 6);
                 tc_fence_after_sync();
-                const int q = q0 + row;
+                const int q = q0 - TILE + row;
                 float* dq_row = dq_bh + (int64_t)q * a.dq_sM + part * 32;
                 tmem_ld32(trow + COL_DQ + part * 32, rs);
                 tmem_wait_ld();
@@ -425,7 +429,42 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                         red_add_v4(dq_row + i, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]),
                                    __uint_as_float(rs[i + 2]), __uint_as_float(rs[i + 3]));
                 }
-                stamp(a, tlc, it, 1, 7);
+            }
+
+            // dS into shared memory (MN-major A operand of dQ = dS K), over the MN-major Q/dO copies once dV/dK
+            // have consumed them: box `part` holds query columns 32*part..32*part+31, one 128-byte row per key
+            // row, 32-byte chunks XOR-swizzled with (row & 3)
+            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.b_done, it & 1, W_BDONE, it));
+            if (!ok) break;
+            stamp(a, tlc, it, 1, 6);
+            {
+                uint8_t* drow = sdS + part * BOX_BYTES + row * 128;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    uint4 v = make_uint4(rp[4 * t], rp[4 * t + 1], rp[4 * t + 2], rp[4 * t + 3]);
+                    *reinterpret_cast<uint4*>(drow + ((((t >> 1) ^ (row & 3)) << 5) | ((t & 1) << 4))) = v;
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&sh.ds_ready);
+            stamp(a, tlc, it, 1, 7);
+        }
+
+        // dQ of the last query tile
+        if (ok && n_it > 0 && part < 2) {
+            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (n_it - 1) & 1, W_DQFULL, n_it - 1));
+            if (ok) {
+                tc_fence_after_sync();
+                const int q = (it0 + n_it - 1) * TILE + row;
+                float* dq_row = dq_bh + (int64_t)q * a.dq_sM + part * 32;
+                tmem_ld32(trow + COL_DQ + part * 32, rs);
+                tmem_wait_ld();
+                if (q < a.Tq) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        red_add_v4(dq_row + i, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]),
+                                   __uint_as_float(rs[i + 2]), __uint_as_float(rs[i + 3]));
+                }
             }
         }
 
