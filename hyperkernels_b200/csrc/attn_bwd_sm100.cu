@@ -336,15 +336,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             // dropout keep bits of this thread's 32 (query, key) pairs
             uint32_t keep = 0xffffffffu;
             if (a.dropout_mode == 2) {
+                // One Philox call covers the eight keys kpos & ~7 .. of one query row, i.e. the key rows of eight
+                // adjacent lanes (k_pos0 and kv0 are multiples of 8, so row & 7 == lane & 7).  Lane j of such a
+                // group evaluates the query columns 8m + j (m = 0..3) and keeps 8 bits per call; the group then
+                // swaps them with shuffles, so every lane does 4 calls for its 32 columns instead of 32.
+                const int j8 = lane & 7;
+                const uint32_t kgrp = (uint32_t)(a.k_pos0 + kvrow) >> 3;
+                uint32_t mine = 0u;  // bit 8m + u: query column c0 + 8m + j8, key row (row & ~7) + u
+#pragma unroll
+                for (int mI = 0; mI < 4; ++mI) {
+                    const hk_philox4_t w = hk_philox_row8(a.seed, a.offset, (uint32_t)bh,
+                                                          (uint32_t)(a.q_pos0 + q0 + c0 + 8 * mI + j8), kgrp);
+                    mine |= hk_philox_keep8(w, a.drop_thr) << (8 * mI);
+                }
                 keep = 0u;
-                const uint32_t kpos = (uint32_t)(a.k_pos0 + kvrow);
-                const uint32_t sel = kpos & 3u;
-#pragma unroll 4
-                for (int i = 0; i < 32; ++i) {
-                    hk_philox4_t w = hk_philox_row4(a.seed, a.offset, (uint32_t)bh, (uint32_t)(a.q_pos0 + q0 + c0 + i),
-                                                    kpos >> 2);
-                    const uint32_t word = sel == 0 ? w.v[0] : sel == 1 ? w.v[1] : sel == 2 ? w.v[2] : w.v[3];
-                    keep |= ((word >= a.drop_thr) ? 1u : 0u) << i;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t other = __shfl_sync(0xffffffffu, mine, (lane & ~7) | j);  // lane j's columns 8m + j
+                    keep |= ((other >> j8) & 0x01010101u) << j;                              // its bit for MY key row
                 }
             } else if (a.dropout_mode == 1) {
                 keep = 0u;

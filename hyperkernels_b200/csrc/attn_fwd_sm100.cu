@@ -342,16 +342,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     r[i + 3] = tf32_round_bits_mma(__float_as_uint(p3));
                 }
             } else if (a.dropout_mode == 2) {
+                // one Philox call per eight keys of this row
 #pragma unroll
-                for (int g = 0; g < 32; ++g) {
-                    const uint32_t kpos = (uint32_t)(a.k_pos0 + kv0 + g * 4);
-                    hk_philox4_t w = hk_philox_row4(a.seed, a.offset, (uint32_t)bh, (uint32_t)(a.q_pos0 + qrow), kpos >> 2);
+                for (int g = 0; g < 16; ++g) {
+                    const uint32_t kpos = (uint32_t)(a.k_pos0 + kv0 + g * 8);
+                    const hk_philox4_t w = hk_philox_row8(a.seed, a.offset, (uint32_t)bh, (uint32_t)(a.q_pos0 + qrow), kpos >> 3);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        float p = ex2_approx(fmaf(__uint_as_float(r[g * 4 + u]), c, neg_m));
-                        if (w.v[u] < a.drop_thr) p = 0.f;
-                        s0 += p;
-                        r[g * 4 + u] = tf32_round_bits_mma(__float_as_uint(p));
+                    for (int u = 0; u < 8; ++u) {
+                        float p = ex2_approx(fmaf(__uint_as_float(r[g * 8 + u]), c, neg_m));
+                        const uint32_t half = (u & 1) ? (w.v[u >> 1] >> 16) : (w.v[u >> 1] & 0xFFFFu);
+                        if (half < a.drop_thr) p = 0.f;
+                        if (u & 1) s1 += p; else s0 += p;
+                        r[g * 8 + u] = tf32_round_bits_mma(__float_as_uint(p));
                     }
                 }
             } else {

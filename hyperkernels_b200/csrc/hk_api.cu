@@ -220,7 +220,7 @@ static int validate_dropout(float p, const float* mask, uint32_t flags, int64_t 
     if (philox && mask) return HK_ERR_BAD_DROPOUT;
     if (p > 0.f) {
         if (philox) {
-            if (k_pos0 % 4 != 0) return HK_ERR_UNSUPPORTED;
+            if (k_pos0 % 8 != 0) return HK_ERR_UNSUPPORTED;  // one Philox call covers keys 8n .. 8n+7
             *mode = 2;
         } else if (mask) {
             *mode = 1;  // reference semantics: active only when p > 0 and mask != nullptr

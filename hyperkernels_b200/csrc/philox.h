@@ -9,10 +9,12 @@
  * mask, so the two agree bit for bit (integer arithmetic only).
  *
  * Element (bh, qi, kj) -- qi and kj are GLOBAL sequence positions -- draws from
- *   counter = { kj >> 2, qi, bh, lo32(offset) }
+ *   counter = { kj >> 3, qi, bh, lo32(offset) }
  *   key     = { lo32(seed), hi32(seed) ^ hi32(offset) }
- * and uses output word (kj & 3), so one Philox call covers four consecutive
- * keys of a query row.  keep <=> word >= floor(p * 2^32).
+ * and uses 16-bit half number (kj & 7) of the 128 output bits (half h of word
+ * (kj & 7) >> 1, low half first), so one Philox call covers eight consecutive
+ * keys of a query row.  keep <=> half >= floor(p * 2^16): the drop probability
+ * is p rounded down to a multiple of 2^-16.
  */
 #ifndef HK_PHILOX_H_
 #define HK_PHILOX_H_
@@ -62,23 +64,36 @@ HK_HD hk_philox4_t hk_philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint3
     return out;
 }
 
-/* floor(p * 2^32) clamped to 32 bits; p in [0,1). */
+/* floor(p * 2^16), in [0, 65535]; p in [0,1). */
 HK_HD uint32_t hk_philox_threshold(float p) {
-    double t = (double)p * 4294967296.0;
+    double t = (double)p * 65536.0;
     if (t <= 0.0) return 0u;
-    if (t >= 4294967295.0) return 4294967295u;
+    if (t >= 65535.0) return 65535u;
     return (uint32_t)t;
 }
 
-/* The four keep words for keys 4*(kj>>2) .. 4*(kj>>2)+3 of query row qi. */
-HK_HD hk_philox4_t hk_philox_row4(uint64_t seed, uint64_t offset, uint32_t bh, uint32_t qi, uint32_t kj4) {
-    return hk_philox4x32_10(kj4, qi, bh, (uint32_t)offset, (uint32_t)seed,
+/* The 128 random bits for keys 8*kj8 .. 8*kj8+7 of query row qi. */
+HK_HD hk_philox4_t hk_philox_row8(uint64_t seed, uint64_t offset, uint32_t bh, uint32_t qi, uint32_t kj8) {
+    return hk_philox4x32_10(kj8, qi, bh, (uint32_t)offset, (uint32_t)seed,
                             (uint32_t)(seed >> 32) ^ (uint32_t)(offset >> 32));
 }
 
+/* Keep bits of the eight keys of one Philox call: bit u <=> key 8*kj8+u is kept. */
+HK_HD uint32_t hk_philox_keep8(hk_philox4_t r, uint32_t thr) {
+    uint32_t m = 0;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+    for (int w = 0; w < 4; ++w) {
+        m |= ((r.v[w] & 0xFFFFu) >= thr ? 1u : 0u) << (2 * w);
+        m |= ((r.v[w] >> 16) >= thr ? 1u : 0u) << (2 * w + 1);
+    }
+    return m;
+}
+
 HK_HD int hk_philox_keep(uint64_t seed, uint64_t offset, uint32_t bh, uint32_t qi, uint32_t kj, uint32_t thr) {
-    hk_philox4_t r = hk_philox_row4(seed, offset, bh, qi, kj >> 2);
-    return r.v[kj & 3u] >= thr;
+    hk_philox4_t r = hk_philox_row8(seed, offset, bh, qi, kj >> 3);
+    return (int)((hk_philox_keep8(r, thr) >> (kj & 7u)) & 1u);
 }
 
 #endif /* HK_PHILOX_H_ */

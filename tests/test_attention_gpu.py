@@ -156,11 +156,13 @@ def _subset_check(B, H, N, causal, p, sigma, heads, seed):
 
 
 def _philox_mask_numpy(bh, Tq, Tk, p, seed, offset, q_pos0=0, k_pos0=0):
-    """Vectorised numpy Philox4x32-10, identical to csrc/philox.h (checked against it in test_dropout_mask_bit_exact)."""
+    """Vectorised numpy Philox4x32-10 keep-mask, identical to csrc/philox.h (checked against it in
+    test_dropout_mask_bit_exact): counter {k >> 3, q, bh, lo32(offset)}, 16-bit half number k & 7."""
     M0, M1, W0, W1 = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85
+    assert k_pos0 % 8 == 0
     qi = (np.arange(Tq, dtype=np.uint64) + q_pos0)[:, None]
-    k4 = ((np.arange((Tk + 3) // 4 + 1, dtype=np.uint64) + (k_pos0 >> 2)))[None, :]
-    c0 = np.broadcast_to(k4, (Tq, k4.shape[1])).astype(np.uint64)
+    k8 = (np.arange((Tk + 7) // 8, dtype=np.uint64) + (k_pos0 >> 3))[None, :]
+    c0 = np.broadcast_to(k8, (Tq, k8.shape[1])).astype(np.uint64)
     c1 = np.broadcast_to(qi, c0.shape).astype(np.uint64)
     c2 = np.full(c0.shape, bh, np.uint64)
     c3 = np.full(c0.shape, offset & 0xFFFFFFFF, np.uint64)
@@ -176,11 +178,10 @@ def _philox_mask_numpy(bh, Tq, Tk, p, seed, offset, q_pos0=0, k_pos0=0):
         c0, c1, c2, c3 = n0, lo1, n2, lo0
         k0 = (k0 + W0) & 0xFFFFFFFF
         k1 = (k1 + W1) & 0xFFFFFFFF
-    words = np.stack([c0, c1, c2, c3], axis=-1).reshape(Tq, -1)  # word index = 4*(k>>2 - k_pos0>>2) + (k&3)
-    start = k_pos0 & 3
-    words = words[:, start:start + Tk]
-    thr = min(int(np.float32(p).astype(np.float64) * 4294967296.0), 4294967295)
-    return (words >= np.uint64(thr)).astype(np.float32)[None]
+    words = np.stack([c0, c1, c2, c3], axis=-1)  # [Tq, groups, 4]
+    halves = np.stack([words & np.uint64(0xFFFF), words >> np.uint64(16)], axis=-1).reshape(Tq, -1)[:, :Tk]
+    thr = min(int(np.float32(p).astype(np.float64) * 65536.0), 65535)
+    return (halves >= np.uint64(thr)).astype(np.float32)[None]
 
 
 def test_config3_noncausal_dropout_subset():

@@ -1,0 +1,122 @@
+"""GPU comparison with the reference's OWN kernels: the three sm_89 attention kernels of
+BlubridgeAI/HyperKernels, unmodified, recompiled for the local GPU into oracle/_ref/libhkref.so (only where the
+reference sources were available at build time; skipped otherwise).  They are fed the very argument block that
+hk_attn_forward / hk_attn_backward receive (the first 192 / 328 bytes are the reference layout), which shows the
+drop-in property, and their error against the CPU oracle is the accuracy ceiling: ours must be no worse."""
+import ctypes as C
+import time
+
+import numpy as np
+import pytest
+import torch
+
+import hyperkernels_b200 as hk
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+SCALE = 0.125
+
+
+def _blocks(Q, K, V, O, LSE, dO, D, dQ, dK, dV, causal):
+    B, H, T, _ = Q.shape
+    f = hk.MemEfficientFwdParams()
+    f.Q, f.K, f.V, f.O, f.LSE = (t.data_ptr() for t in (Q, K, V, O, LSE))
+    f.B, f.nh, f.T, f.scale, f.is_causal = B, H, T, SCALE, causal
+    b = hk.MemEfficientBwdParams()
+    b.Q, b.K, b.V, b.O, b.dO, b.LSE, b.D, b.dQ, b.dK, b.dV = (t.data_ptr() for t in (Q, K, V, O, dO, LSE, D, dQ, dK, dV))
+    b.B, b.nh, b.T, b.scale, b.is_causal = B, H, T, SCALE, causal
+    for blk, names in ((f, "qkvo"), (b, ("q", "k", "v", "o", "do", "dq", "dk", "dv"))):
+        for n in names:
+            setattr(blk, f"{n}_strideB", H * T * 64); setattr(blk, f"{n}_strideH", T * 64); setattr(blk, f"{n}_strideM", 64)
+        blk.lse_strideB, blk.lse_strideH = H * T, T
+    b.d_strideB, b.d_strideH = H * T, T
+    return f, b
+
+
+@pytest.mark.skipif(ol.reference() is None, reason="oracle/_ref not built (reference sources absent at build time)")
+@pytest.mark.parametrize("causal", [False, True])
+def test_no_worse_than_the_reference_kernels(causal):
+    ref = ol.reference()
+    B, H, T = 2, 4, 512
+    rng = np.random.default_rng(21)
+    Q, K, V, dO = (rng.standard_normal((B, H, T, 64)).astype(np.float32) for _ in range(4))
+    O_or, L_or = ol.attn_forward_mt(Q, K, V, SCALE, int(causal))
+    D_or, dQ_or, dK_or, dV_or = ol.attn_backward_mt(Q, K, V, O_or, dO, L_or, SCALE, int(causal))
+    t = {k: torch.from_numpy(v).cuda() for k, v in dict(Q=Q, K=K, V=V, dO=dO).items()}
+    mk = lambda: torch.empty((B, H, T, 64), device="cuda")
+    O, dQ, dK, dV = mk(), torch.zeros((B, H, T, 64), device="cuda"), mk(), mk()
+    LSE, D = torch.empty((B, H, T), device="cuda"), torch.empty((B, H, T), device="cuda")
+    f, b = _blocks(t["Q"], t["K"], t["V"], O, LSE, t["dO"], D, dQ, dK, dV, causal)
+    # --- the reference kernels, launched with the reference test's geometry (kernels_test.cu:509-530,475-477,580-584)
+    assert ref.hkref_gpu_forward(C.byref(f), None) == 0
+    assert ref.hkref_gpu_precompute_D(C.byref(b), None) == 0
+    assert ref.hkref_gpu_backward(C.byref(b), None) == 0
+    torch.cuda.synchronize()
+    ref_err = {k: (ol.max_abs(v.cpu().numpy(), o), ol.rel_l2(v.cpu().numpy(), o))
+               for k, v, o in (("O", O, O_or), ("dQ", dQ, dQ_or), ("dK", dK, dK_or), ("dV", dV, dV_or))}
+    # --- ours, same argument blocks plus a workspace
+    O2, dQ2, dK2, dV2 = mk(), mk(), mk(), mk()
+    LSE2, D2 = torch.empty((B, H, T), device="cuda"), torch.empty((B, H, T), device="cuda")
+    f2, b2 = _blocks(t["Q"], t["K"], t["V"], O2, LSE2, t["dO"], D2, dQ2, dK2, dV2, causal)
+    ws = torch.empty(4 * B * H * T * 256 + 256, dtype=torch.uint8, device="cuda")
+    base = ws.data_ptr() + (-ws.data_ptr()) % 256
+    f2.workspace, f2.workspace_bytes = base, hk.fwd_workspace_bytes(f2)
+    b2.workspace, b2.workspace_bytes = base, hk.bwd_workspace_bytes(b2)
+    hk.fused_attn_forward(f2)
+    hk.mem_efficient_bwd_unified(b2)
+    torch.cuda.synchronize()
+    assert hk.last_device_status() == 0
+    our_err = {k: (ol.max_abs(v.cpu().numpy(), o), ol.rel_l2(v.cpu().numpy(), o))
+               for k, v, o in (("O", O2, O_or), ("dQ", dQ2, dQ_or), ("dK", dK2, dK_or), ("dV", dV2, dV_or))}
+    print("reference kernels:", ref_err)
+    print("sm_100a kernels:  ", our_err)
+    for k in ref_err:
+        # same rounding of every MMA operand, same fp32 accumulation: errors of the same size (25 % slack for the
+        # different summation order and exp2 approximation), and inside the absolute gate
+        assert our_err[k][1] <= max(1.25 * ref_err[k][1], 2e-4), (k, our_err[k], ref_err[k])
+        assert our_err[k][0] <= 5e-3 and our_err[k][1] <= 1e-3
+
+
+@pytest.mark.skipif(ol.reference() is None, reason="oracle/_ref not built (reference sources absent at build time)")
+def test_speed_against_the_reference_kernels_on_this_gpu(capsys):
+    """Not a gate: prints the time of the reference's kernels and ours at the GPT-2-small shape on this GPU."""
+    ref = ol.reference()
+    B, H, T = 8, 12, 1024
+    g = torch.Generator(device="cuda").manual_seed(3)
+    Q, K, V, dO = (torch.randn((B, H, T, 64), generator=g, device="cuda") for _ in range(4))
+    mk = lambda: torch.empty((B, H, T, 64), device="cuda")
+    O, dQ, dK, dV = mk(), mk(), mk(), mk()
+    LSE, D = torch.empty((B, H, T), device="cuda"), torch.empty((B, H, T), device="cuda")
+    f, b = _blocks(Q, K, V, O, LSE, dO, D, dQ, dK, dV, True)
+
+    def timed(fn, n=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(e) / n
+
+    def ref_step():
+        ref.hkref_gpu_forward(C.byref(f), None)
+        ref.hkref_gpu_precompute_D(C.byref(b), None)
+        dQ.zero_()
+        ref.hkref_gpu_backward(C.byref(b), None)
+
+    ws = torch.empty(4 * B * H * T * 256 + 256, dtype=torch.uint8, device="cuda")
+
+    def our_step():
+        hk.attention_forward(Q, K, V, SCALE, True, workspace=ws, out=O, lse=LSE)
+        hk.attention_backward(Q, K, V, O, dO, LSE, SCALE, True, workspace=ws, D=D, dQ=dQ, dK=dK, dV=dV, reuse_fwd_rounded=True)
+
+    t_ref, t_our = timed(ref_step), timed(our_step)
+    flop = 14 * B * H * T * T * 64 / 2
+    with capsys.disabled():
+        print(f"\n[B200, B8 H12 N1024 causal fwd+bwd] reference sm_89 kernels recompiled: {t_ref:.3f} ms "
+              f"({flop / t_ref / 1e9:.1f} TFLOP/s); sm_100a kernels: {t_our:.3f} ms ({flop / t_our / 1e9:.1f} TFLOP/s); "
+              f"ratio {t_ref / t_our:.2f}x")
+    assert hk.last_device_status() == 0
