@@ -305,8 +305,9 @@ def run_ours(args, cfg, rank, local_rank, world):
         line = {
             "metric": METRIC, "value": total / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
-            "config": {"workload": cfg["name"] + (" per GPU" if world > 1 else ""), "config_id": args.config,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+            "config": {"workload": cfg["name"] + (" per GPU" if world > 1 and args.scaling == "weak" else ""),
+                       "config_id": args.config,
                        "l2": "256 MiB buffer written between timed steps (untimed)",
                        "step": "hk_attn_forward + hk_attn_backward (TF32 rounding pre-pass once per step, D pre-pass + dQ zeroing, main kernels)",
                        "partition": "batch x head across GPUs, no collective"},
@@ -457,11 +458,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ring", type=int, default=2, help="config 5 on N > 1 GPUs: ranks per sequence ring")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every rank runs a whole batch of the config; strong: the config's batch is split over the ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.scaling == "strong" and world > 1 and args.config != 5:
+        assert cfg["B"] % world == 0, "strong scaling splits the batch dimension evenly"
+        cfg["B"] //= world
+        cfg["name"] += f" split over {world} GPUs by batch"
     if args.impl == "reference":
         run_reference(args, cfg, rank, world)
     elif args.config == 5 and world > 1:

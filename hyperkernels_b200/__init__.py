@@ -22,6 +22,7 @@ from .attention import (  # noqa: F401
     mem_efficient_bwd_precompute_D,
     mem_efficient_bwd_unified,
     merge_partial,
+    round_tf32,
     FLAG_PHILOX_DROPOUT,
     FLAG_OPERANDS_PREROUNDED,
     FLAG_ACCUM_DKDV,

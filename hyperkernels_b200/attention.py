@@ -125,6 +125,7 @@ def lib() -> C.CDLL:
                                            C.c_uint64, C.c_int64, C.c_int64]
         L.hk_attn_last_device_status.restype = C.c_int
         L.hk_attn_launch_count.restype = C.c_uint64
+        L.hk_attn_round_tf32.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         L.hk_attn_selftest.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         _lib = L
     return _lib
@@ -299,6 +300,17 @@ def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropo
         p.workspace, p.workspace_bytes = ws[1], bwd_workspace_bytes(p)
     mem_efficient_bwd_unified(p, stream)
     return dQ, dK, dV, D
+
+
+def round_tf32(x, out=None, stream=None):
+    """TF32-round a contiguous [..., 64] fp32 CUDA tensor the way the kernels' pre-pass does."""
+    import torch
+
+    assert x.is_contiguous() and x.shape[-1] == 64
+    out = out if out is not None else torch.empty_like(x)
+    _check(lib().hk_attn_round_tf32(x.data_ptr(), out.data_ptr(), x.numel() // 64, _stream_handle(stream)),
+           "hk_attn_round_tf32")
+    return out
 
 
 def merge_partial(O_acc, LSE_acc, O_part, LSE_part, stream=None) -> None:

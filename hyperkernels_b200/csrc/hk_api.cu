@@ -441,6 +441,18 @@ int hk_attn_selftest(int which, const float* A, const float* B, float* out, void
     return run_umma_selftest(which, A, B, out, static_cast<cudaStream_t>(stream_));
 }
 
+int hk_attn_round_tf32(const float* src, float* dst, int64_t rows, void* stream_) {
+    if (!src || !dst) return HK_ERR_NULL_POINTER;
+    if (rows < 0 || rows > (1LL << 31) - 1) return HK_ERR_BAD_SHAPE;
+    if (!aligned16(src) || !aligned16(dst)) return HK_ERR_MISALIGNED;
+    RoundJob job{};
+    job.src[0] = View4{src, 0, 64, 0};  // one "head" of `rows` contiguous rows
+    job.dst[0] = dst;
+    job.T[0] = (int)rows;
+    job.H = 1; job.BH = 1; job.n = 1;
+    return launch_round_tf32(job, static_cast<cudaStream_t>(stream_));
+}
+
 void hk_attn_debug_timeline(long long* device_buffer, int block) {
     g_timeline = device_buffer;
     g_timeline_block = block;

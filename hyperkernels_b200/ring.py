@@ -54,8 +54,13 @@ class CudaBackend:
 
         self.att = att
 
+    def prepare(self, x):
+        """TF32-round a shard once, so that the per-pair calls can skip their rounding pre-pass (a K/V block is
+        rounded by its owner and travels rounded)."""
+        return self.att.round_tf32(x.contiguous())
+
     def fwd(self, Q, K, V, scale, causal, q_pos0, k_pos0):
-        return self.att.attention_forward(Q, K, V, scale, causal, q_pos0=q_pos0, k_pos0=k_pos0)
+        return self.att.attention_forward(Q, K, V, scale, causal, q_pos0=q_pos0, k_pos0=k_pos0, prerounded=True)
 
     def merge(self, O_acc, LSE_acc, O_part, LSE_part):
         self.att.merge_partial(O_acc, LSE_acc, O_part, LSE_part)
@@ -74,12 +79,12 @@ class CudaBackend:
         self.att.mem_efficient_bwd_precompute_D(p)
         return D
 
-    def bwd(self, Q, K, V, O, dO, LSE, D, scale, causal, q_pos0, k_pos0, dQ):
-        """Adds this pair's contribution into dQ (in place); returns the pair's (dK, dV).
+    def bwd(self, Q, K, V, O, dO, LSE, D, scale, causal, q_pos0, k_pos0, dQ, dK, dV):
+        """Adds this pair's contributions into dQ, dK and dV (all in place, kernel-side accumulation).
         D = rowsum(dO * O) of the FINAL output is passed in, so O itself is not needed here."""
-        _, dK, dV, _ = self.att.attention_backward(Q, K, V, None, dO, LSE, scale, causal, q_pos0=q_pos0, k_pos0=k_pos0,
-                                                   D=D, d_precomputed=True, accum_dq=True, dQ=dQ)
-        return dK, dV
+        self.att.attention_backward(Q, K, V, None, dO, LSE, scale, causal, q_pos0=q_pos0, k_pos0=k_pos0, D=D,
+                                    d_precomputed=True, accum_dq=True, accum_dkdv=True, dQ=dQ, dK=dK, dV=dV,
+                                    prerounded=True)
 
 
 class RingAttention:
@@ -137,6 +142,7 @@ class RingAttention:
     # ---- forward ------------------------------------------------------------------
     def forward(self, Q, K, V):
         G = self.world
+        Q, K, V = self.backend.prepare(Q), self.backend.prepare(K), self.backend.prepare(V)
         q_views = self._seg_views(Q, self.my_segs)
         O_acc = [torch.zeros(v.shape, dtype=torch.float32, device=Q.device) for v in q_views]
         LSE_acc = [torch.full(v.shape[:3], float("-inf"), dtype=torch.float32, device=Q.device) for v in q_views]
@@ -165,6 +171,7 @@ class RingAttention:
     def backward(self, Q, K, V, O, LSE, dO):
         G = self.world
         D = self.backend.precompute_D(dO.contiguous(), O.contiguous())
+        Q, K, V, dO = (self.backend.prepare(x) for x in (Q, K, V, dO))
         q_views = self._seg_views(Q, self.my_segs)
         do_views = self._seg_views(dO, self.my_segs)
         o_views = self._seg_views(O, self.my_segs)
@@ -191,11 +198,9 @@ class RingAttention:
                 for ki, kseg in enumerate(src_segs):
                     if not visible(qseg, kseg, self.causal):
                         continue
-                    dK_p, dV_p = self.backend.bwd(q_views[qi], k_views[ki], v_views[ki], o_views[qi], do_views[qi],
-                                                  lse_views[qi], d_views[qi], self.scale, self.causal, qseg[0], kseg[0],
-                                                  dq_views[qi])
-                    pk_views[ki].add_(dK_p)
-                    pv_views[ki].add_(dV_p)
+                    self.backend.bwd(q_views[qi], k_views[ki], v_views[ki], o_views[qi], do_views[qi], lse_views[qi],
+                                     d_views[qi], self.scale, self.causal, qseg[0], kseg[0], dq_views[qi], pk_views[ki],
+                                     pv_views[ki])
             # the accumulator of this block left the previous rank one step ago
             if t > 0:
                 self._finish(acc_handle)

@@ -194,6 +194,12 @@ size_t hk_attn_bwd_workspace_bytes(const hk_attn_bwd_params* p);
 int hk_attn_merge_partial(float* O_acc, float* LSE_acc, const float* O_part, const float* LSE_part, int64_t rows,
                           void* stream);
 
+/* Rounds `rows` contiguous rows of 64 floats to TF32 (round to nearest, the reference's
+ * `+0x1000`, fused_attn_forward_kernel_tc_sm89.cu:197) from src into dst (may alias).  A caller
+ * that feeds the same tensor to several calls (the ring schedule does) rounds it once and passes
+ * HK_FLAG_OPERANDS_PREROUNDED.  No counterpart in the reference, which rounds at every load. */
+int hk_attn_round_tf32(const float* src, float* dst, int64_t rows, void* stream);
+
 /* Host twin of the in-kernel Philox keep-mask: fills the dense mask the
  * reference forward consumes (fused_attn_forward_kernel_tc_sm89.cu:321-324),
  * mask[(bh*Tq + i)*Tk + j] = 1.0f keep / 0.0f drop.  `mask` is HOST memory. */

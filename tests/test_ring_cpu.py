@@ -31,6 +31,9 @@ class OracleBackend:
     def _np(t):
         return np.ascontiguousarray(t.detach().cpu().numpy(), dtype=np.float32)
 
+    def prepare(self, x):
+        return x.contiguous()
+
     def fwd(self, Q, K, V, scale, causal, q_pos0, k_pos0):
         O, L = self.ol.attn_forward(self._np(Q), self._np(K), self._np(V), scale, int(causal), None, q_pos0, k_pos0)
         return torch.from_numpy(O), torch.from_numpy(L)
@@ -49,11 +52,12 @@ class OracleBackend:
     def precompute_D(self, dO, O):
         return torch.from_numpy(self.ol.precompute_D(self._np(dO), self._np(O)))
 
-    def bwd(self, Q, K, V, O, dO, LSE, D, scale, causal, q_pos0, k_pos0, dQ):
+    def bwd(self, Q, K, V, O, dO, LSE, D, scale, causal, q_pos0, k_pos0, dQ, dK, dV):
         _, dq, dk, dv = self.ol.attn_backward(self._np(Q), self._np(K), self._np(V), self._np(O), self._np(dO),
                                               self._np(LSE), scale, int(causal), None, q_pos0, k_pos0)
         dQ.add_(torch.from_numpy(dq))
-        return torch.from_numpy(dk), torch.from_numpy(dv)
+        dK.add_(torch.from_numpy(dk))
+        dV.add_(torch.from_numpy(dv))
 
 
 def _gather_seq(x_local, segs_all, T):
