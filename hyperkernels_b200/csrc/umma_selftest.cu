@@ -8,6 +8,9 @@
 //   case 0  D[128,128] = A[128,64] * B[128,64]^T    A, B K-major in smem (S = Q K^T)
 //   case 1  D[128,64]  = A[128,128] * B[128,64]     A in tensor memory, B MN-major (O = P V)
 //   case 2  D[128,64]  = A[128,128]^T * B[128,64]   A MN-major in smem, B MN-major (dQ = dS K)
+//   case 3  no product: one thread waits on an mbarrier that nothing ever arrives at, to show that
+//           a wait that cannot complete ends after HK_WAIT_LIMIT_NS with the device status word
+//           set (hk_attn_last_device_status -> HK_ERR_DEVICE_TIMEOUT) and the context still usable
 #include "attn_kernels.cuh"
 
 namespace hk {
@@ -49,6 +52,19 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     WaitCtx wc{&sh.abort_flag, status};
     const int N = (which == 0) ? 128 : 64;
     uint32_t r[32];
+
+    if (which == 3) {
+        // nothing is in flight: the only thing to wind down after the failed wait is tensor memory
+        if (threadIdx.x == 0) mbar_wait(wc, &sh.full, 0, 999);
+        tc_fence_before_sync();
+        __syncthreads();
+        if (warp == 0) {
+            __syncwarp();
+            tc_fence_after_sync();
+            tmem_dealloc(tmem, 256);
+        }
+        return;
+    }
 
     if (which == 1) {
         // stage A into tensor-memory columns 128..255 (lane = row)
@@ -212,7 +228,7 @@ int run_umma_peak(int mode, int iters, int ctas, const float* A, const float* B,
 }
 
 int run_umma_selftest(int which, const float* A, const float* B, float* out, cudaStream_t stream) {
-    if (which < 0 || which > 2) return HK_ERR_UNSUPPORTED;
+    if (which < 0 || which > 3) return HK_ERR_UNSUPPORTED;
     if (!A || !B || !out) return HK_ERR_NULL_POINTER;
     CUtensorMap ma, mb;
     int rc;

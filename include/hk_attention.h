@@ -225,7 +225,10 @@ int hk_attn_kernel_timing_read(int kind, double* total_ms, int* launches);
 /* Runs the tensor-core self-test on the current device: small TF32 products
  * through each operand path the attention kernels use (K-major and MN-major
  * shared-memory operands, tensor-memory A operand).  out[0..n) receives the
- * raw results of case `which`; see hyperkernels_b200/csrc/umma_selftest.cu. */
+ * raw results of case `which` (0..2); case 3 computes nothing and makes one
+ * bounded wait run out on purpose (about 2 s), after which
+ * hk_attn_last_device_status() reports HK_ERR_DEVICE_TIMEOUT once; see
+ * hyperkernels_b200/csrc/umma_selftest.cu. */
 int hk_attn_selftest(int which, const float* A, const float* B, float* out, void* stream);
 
 /* Performance debugging: while `device_buffer` (device memory, 4096 int64) is set, CTA

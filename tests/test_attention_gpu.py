@@ -453,3 +453,26 @@ def test_long_sequence_rows_against_oracle():
                                                q_pos0=k0, k_pos0=k0)
     assert ol.rel_l2(host(dK[:, :, k0:k0 + 128]), dK_ref) <= 5e-3
     assert ol.rel_l2(host(dV[:, :, k0:k0 + 128]), dV_ref) <= 5e-3
+
+
+# ---------------------------------------------------------------------------
+# failure detection: a wait that cannot complete ends by itself and is reported
+# ---------------------------------------------------------------------------
+def test_bounded_wait_reports_timeout_and_context_survives():
+    """Self-test case 3 waits on an mbarrier nothing arrives at.  No fault, no trap: the wait gives up after its
+    limit (2 s), the kernel frees its tensor memory and returns, the status word says so once, and the next
+    kernels run normally."""
+    import time
+
+    L = hk.lib()
+    z = torch.zeros(128 * 128, device="cuda")
+    t0 = time.time()
+    assert L.hk_attn_selftest(3, z.data_ptr(), z.data_ptr(), z.data_ptr(), None) == 0
+    assert hk.last_device_status() == -8  # HK_ERR_DEVICE_TIMEOUT (synchronises)
+    assert 1.5 < time.time() - t0 < 10.0
+    assert hk.last_device_status() == 0  # reported once, then cleared
+    Q, K, V = (dev(normal((1, 2, 256, 64), 300 + s)) for s in range(3))
+    O, LSE = hk.attention_forward(Q, K, V, SCALE, True)
+    ok_status()
+    O_ref, _ = ol.attn_forward_mt(host(Q), host(K), host(V), SCALE, 1)
+    gate("O", host(O), O_ref)
