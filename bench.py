@@ -266,6 +266,14 @@ def run_ours(args, cfg, rank, local_rank, world):
         L.hk_attn_kernel_timing_read(kind, C.byref(tot), C.byref(n))
         kt[name] = tot.value / max(n.value, 1)
     assert hk.last_device_status() == 0, "a bounded wait inside a kernel gave up"
+    # the same K steps back to back, without the flush (the reference reports flushed numbers; this one is extra)
+    ev_hot = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    ev_hot[0].record(stream)
+    for _ in range(args.steps):
+        step()
+    ev_hot[1].record(stream)
+    torch.cuda.synchronize()
+    ms_hot = ev_hot[0].elapsed_time(ev_hot[1]) / args.steps
 
     # ---- end to end through the C ABI with host buffers ----------------------------
     hQ, hK, hV, hdO = (t.cpu().pin_memory() for t in (Q, K, V, dO))
@@ -324,6 +332,7 @@ def run_ours(args, cfg, rank, local_rank, world):
             "gpu_launches": int(launches),
             "clocks": clk,
             "wall_s_timed_region": t_wall,
+            "ms_per_step_back_to_back_no_flush": ms_hot,
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(cfg)

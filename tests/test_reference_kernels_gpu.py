@@ -34,12 +34,17 @@ def _blocks(Q, K, V, O, LSE, dO, D, dQ, dK, dV, causal):
 
 
 @pytest.mark.skipif(ol.reference() is None, reason="oracle/_ref not built (reference sources absent at build time)")
-@pytest.mark.parametrize("causal", [False, True])
-def test_no_worse_than_the_reference_kernels(causal):
+@pytest.mark.parametrize("causal,stress", [(False, False), (True, False), (True, True)])
+def test_no_worse_than_the_reference_kernels(causal, stress):
+    """stress: every 64th key row scaled x8 as in the long-sequence config, where |scores| reach ~60 and plain TF32
+    cannot meet the absolute gate -- neither kernel does; the applicable bound there is the reference kernel's own
+    error."""
     ref = ol.reference()
     B, H, T = 2, 4, 512
     rng = np.random.default_rng(21)
     Q, K, V, dO = (rng.standard_normal((B, H, T, 64)).astype(np.float32) for _ in range(4))
+    if stress:
+        K[:, :, ::64] *= 8.0
     O_or, L_or = ol.attn_forward_mt(Q, K, V, SCALE, int(causal))
     D_or, dQ_or, dK_or, dV_or = ol.attn_backward_mt(Q, K, V, O_or, dO, L_or, SCALE, int(causal))
     t = {k: torch.from_numpy(v).cuda() for k, v in dict(Q=Q, K=K, V=V, dO=dO).items()}
@@ -74,7 +79,10 @@ def test_no_worse_than_the_reference_kernels(causal):
         # same rounding of every MMA operand, same fp32 accumulation: errors of the same size (25 % slack for the
         # different summation order and exp2 approximation), and inside the absolute gate
         assert our_err[k][1] <= max(1.25 * ref_err[k][1], 2e-4), (k, our_err[k], ref_err[k])
-        assert our_err[k][0] <= 5e-3 and our_err[k][1] <= 1e-3
+        if stress:
+            assert our_err[k][0] <= max(1.25 * ref_err[k][0], 5e-3), (k, our_err[k], ref_err[k])
+        else:
+            assert our_err[k][0] <= 5e-3 and our_err[k][1] <= 1e-3
 
 
 @pytest.mark.skipif(ol.reference() is None, reason="oracle/_ref not built (reference sources absent at build time)")
