@@ -37,6 +37,7 @@ FLAG_ACCUM_DKDV = 1 << 2
 FLAG_ACCUM_DQ = 1 << 3
 FLAG_D_PRECOMPUTED = 1 << 4
 FLAG_REUSE_FWD_ROUNDED = 1 << 5
+FLAG_DROPOUT_SCALED = 1 << 6  # inverted dropout (kept terms / (1 - p), normaliser over all keys)
 
 _f32p = C.POINTER(C.c_float)
 
@@ -216,7 +217,8 @@ def _workspace(nbytes: int, like, workspace):
 
 def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float = 0.0, dropout_mask=None,
                       philox_seed: Optional[int] = None, philox_offset: int = 0, q_pos0: int = 0, k_pos0: int = 0,
-                      prerounded: bool = False, workspace=None, out=None, lse=None, stream=None):
+                      prerounded: bool = False, dropout_scaled: bool = False, workspace=None, out=None, lse=None,
+                      stream=None):
     """O, LSE = fused attention forward of [B,H,Tq,64] Q against [B,H,Tk,64] K, V (fp32 CUDA tensors)."""
     import torch
 
@@ -240,6 +242,8 @@ def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float =
         p.dropout_seed, p.dropout_offset = philox_seed, philox_offset
     if prerounded:
         flags |= FLAG_OPERANDS_PREROUNDED
+    if dropout_scaled:
+        flags |= FLAG_DROPOUT_SCALED
     p.flags = flags
     ws = _workspace(fwd_workspace_bytes(p), Q, workspace)
     if ws is not None:
@@ -251,8 +255,8 @@ def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float =
 def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropout_p: float = 0.0, dropout_mask=None,
                        philox_seed: Optional[int] = None, philox_offset: int = 0, q_pos0: int = 0, k_pos0: int = 0,
                        prerounded: bool = False, D=None, d_precomputed: bool = False, accum_dkdv: bool = False,
-                       accum_dq: bool = False, reuse_fwd_rounded: bool = False, workspace=None, dQ=None, dK=None, dV=None,
-                       stream=None):
+                       accum_dq: bool = False, reuse_fwd_rounded: bool = False, dropout_scaled: bool = False,
+                       workspace=None, dQ=None, dK=None, dV=None, stream=None):
     """dQ, dK, dV, D = fused attention backward (fp32 CUDA tensors, [B,H,T,64])."""
     import torch
 
@@ -291,6 +295,8 @@ def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropo
         flags |= FLAG_ACCUM_DKDV
     if accum_dq:
         flags |= FLAG_ACCUM_DQ
+    if dropout_scaled:
+        flags |= FLAG_DROPOUT_SCALED
     if reuse_fwd_rounded:
         assert workspace is not None, "reuse_fwd_rounded needs the workspace the forward used"
         flags |= FLAG_REUSE_FWD_ROUNDED

@@ -367,9 +367,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 }
             }
             // fold the causal / tail mask into the keep bits: column cc is visible iff cc >= cmin
+            uint32_t vis = 0xffffffffu;
             {
                 const int lo = cmin - c0;  // first visible local index, may be <= 0 or >= 32
-                if (lo > 0) keep &= (lo >= 32) ? 0u : (0xffffffffu << lo);
+                if (lo > 0) vis = (lo >= 32) ? 0u : (0xffffffffu << lo);
+                keep &= vis;
             }
             tmem_wait_ld();
             stamp(a, tlc, it, 1, 3);
@@ -389,8 +391,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     for (int t = 0; t < 4; ++t) {
                         const int i = g * 4 + t;
                         const float p = ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -Ls[t]));
-                        const float ds = p * fmaf(__uint_as_float(rp[i]), a.scale, -Ds[t]);
+                        const float ds = p * fmaf(__uint_as_float(rp[i]), a.dp_scale, -Ds[t]);
                         rs[i] = tf32_round_bits_mma(__float_as_uint(p));
+                        rp[i] = tf32_round_bits_mma(__float_as_uint(ds));
+                    }
+                }
+            } else if (a.drop_scaled) {
+                // inverted dropout: p is the softmax over all visible keys; a dropped pair keeps the -D term of
+                // dS but contributes neither dP nor to dV
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float4 L = lse4[g];
+                    const float4 Dv = ds4[g];
+                    const float Ls[4] = {L.x, L.y, L.z, L.w};
+                    const float Ds[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const int i = g * 4 + t;
+                        float p = ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -Ls[t]));
+                        if (!((vis >> i) & 1u)) p = 0.f;
+                        const bool kept = (keep >> i) & 1u;
+                        const float dp = kept ? __uint_as_float(rp[i]) : 0.f;
+                        const float ds = p * fmaf(dp, a.dp_scale, -Ds[t]);
+                        rs[i] = kept ? tf32_round_bits_mma(__float_as_uint(p)) : 0u;
                         rp[i] = tf32_round_bits_mma(__float_as_uint(ds));
                     }
                 }
@@ -488,6 +511,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         if (ok && n_it > 0) {
             tmem_ld32(trow + col, rs);
             tmem_wait_ld();
+            if (part < 2 && a.dv_scale != 1.f) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) rs[i] = __float_as_uint(__uint_as_float(rs[i]) * a.dv_scale);
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) rs[i] = 0u;

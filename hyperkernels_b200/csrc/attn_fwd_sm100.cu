@@ -261,6 +261,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         const float c = a.scale_log2e;
         const float worst = (c >= 0.f) ? -INFINITY : INFINITY;  // raw score that can never win the max
 
+        const bool scaled = a.drop_scaled != 0;
         float m = -INFINITY;  // running max actually used as exponent reference, log2 units
         float l = 0.f;
         bool ok = true;
@@ -351,6 +352,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     for (int u = 0; u < 8; ++u) {
                         float p = ex2_approx(fmaf(__uint_as_float(r[g * 8 + u]), c, neg_m));
                         const uint32_t half = (u & 1) ? (w.v[u >> 1] >> 16) : (w.v[u >> 1] & 0xFFFFu);
+                        if (scaled) { if (u & 1) s3 += p; else s2 += p; }  // the normaliser ignores the mask
                         if (half < a.drop_thr) p = 0.f;
                         if (u & 1) s1 += p; else s0 += p;
                         r[g * 8 + u] = tf32_round_bits_mma(__float_as_uint(p));
@@ -361,6 +363,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #pragma unroll
                 for (int i = 0; i < 128; ++i) {
                     float p = ex2_approx(fmaf(__uint_as_float(r[i]), c, neg_m));
+                    if (scaled) s2 += (i <= lim_local) ? p : 0.f;
                     p = (i <= lim_local) ? p * __ldg(mrow + i) : 0.f;
                     s0 += p;
                     r[i] = tf32_round_bits_mma(__float_as_uint(p));
@@ -370,7 +373,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tmem_st32p(tS + 32, r + 32);
             tmem_st32p(tS + 64, r + 64);
             tmem_st32p(tS + 96, r + 96);
-            l = l * alpha + ((s0 + s1) + (s2 + s3));
+            // inverted dropout: s2, s3 hold the sums over all visible keys, s0, s1 the kept ones
+            l = l * alpha + ((scaled && a.dropout_mode != 0) ? (s2 + s3) : ((s0 + s1) + (s2 + s3)));
             m = m_new;
             stamp(a, tls, j, 1 + t, 3);
             tmem_wait_st();
@@ -382,7 +386,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         // epilogue: O / l and LSE
         if (ok && nt > 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.o_full[t], (nt - 1) & 1, W_OFULL, nt));
         tc_fence_after_sync();
-        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        const float inv_l = (l > 0.f) ? a.keep_scale / l : 0.f;
         if (ok && nt > 0) {
             tmem_ld32p(tO, r);
             tmem_ld32p(tO + 32, r + 32);

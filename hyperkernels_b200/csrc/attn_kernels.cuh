@@ -16,6 +16,8 @@ struct FwdArgs {
     float scale_log2e;
     int causal;
     int dropout_mode;  // 0 none, 1 dense mask, 2 Philox
+    int drop_scaled;   // 1: inverted dropout (normaliser over all visible keys, kept terms times keep_scale)
+    float keep_scale;  // 1/(1-p) when drop_scaled, else 1
     uint32_t drop_thr;
     uint64_t seed, offset;
     DeviceStatus* status;
@@ -43,6 +45,9 @@ struct BwdArgs {
     int causal;
     int accum_dkdv;
     int dropout_mode;
+    int drop_scaled;   // 1: inverted dropout; p below is then the softmax over all visible keys
+    float dp_scale;    // factor of dP inside dS: scale, times 1/(1-p) when drop_scaled
+    float dv_scale;    // factor of the dV accumulator: 1/(1-p) when drop_scaled, else 1
     uint32_t drop_thr;
     uint64_t seed, offset;
     DeviceStatus* status;

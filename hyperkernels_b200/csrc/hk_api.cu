@@ -213,6 +213,14 @@ size_t hk_attn_bwd_workspace_bytes(const hk_attn_bwd_params* p) {
     return 2 * align_up(bh * p->T * 256, 256) + 2 * align_up(bh * Tk * 256, 256);  // Q, dO, K, V
 }
 
+// 1/(1-p) of the inverted-dropout option, with p as the kernels apply it: the Philox mask drops with
+// probability floor(p * 65536) / 65536, a caller's dense mask is taken to have been drawn with p itself.
+static float keep_scale_of(float p, int mode, uint32_t flags) {
+    if (!(flags & HK_FLAG_DROPOUT_SCALED) || mode == 0) return 1.f;
+    const double pe = (mode == 2) ? (double)hk_philox_threshold(p) / 65536.0 : (double)p;
+    return (float)(1.0 / (1.0 - pe));
+}
+
 static int validate_dropout(float p, const float* mask, uint32_t flags, int64_t k_pos0, int* mode) {
     *mode = 0;
     if (!(p >= 0.f && p < 1.f)) return HK_ERR_BAD_DROPOUT;
@@ -288,6 +296,8 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     a.scale_log2e = p->scale * LOG2E;
     a.causal = p->is_causal ? 1 : 0;
     a.dropout_mode = mode;
+    a.keep_scale = keep_scale_of(p->dropout_p, mode, p->flags);
+    a.drop_scaled = (mode != 0 && (p->flags & HK_FLAG_DROPOUT_SCALED)) ? 1 : 0;
     a.drop_thr = hk_philox_threshold(p->dropout_p);
     a.seed = p->dropout_seed; a.offset = p->dropout_offset;
     a.status = device_status_ptr();
@@ -420,6 +430,9 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     a.causal = p->is_causal ? 1 : 0;
     a.accum_dkdv = (p->flags & HK_FLAG_ACCUM_DKDV) ? 1 : 0;
     a.dropout_mode = mode;
+    a.drop_scaled = (mode != 0 && (p->flags & HK_FLAG_DROPOUT_SCALED)) ? 1 : 0;
+    a.dv_scale = keep_scale_of(p->dropout_p, mode, p->flags);
+    a.dp_scale = p->scale * a.dv_scale;
     a.drop_thr = hk_philox_threshold(p->dropout_p);
     a.seed = p->dropout_seed; a.offset = p->dropout_offset;
     a.status = device_status_ptr();

@@ -69,7 +69,13 @@ enum {
     HK_FLAG_D_PRECOMPUTED = 1u << 4,
     /* backward: `workspace` is the one hk_attn_forward was given for these same Q, K, V
      * (same shapes) and still holds their rounded copies: do not round them again. */
-    HK_FLAG_REUSE_FWD_ROUNDED = 1u << 5
+    HK_FLAG_REUSE_FWD_ROUNDED = 1u << 5,
+    /* forward and backward: inverted dropout instead of the reference's drop-then-renormalise
+     * (no reference counterpart).  The softmax is normalised over ALL visible keys, the kept
+     * probabilities are multiplied by 1/(1-p) and the dropped ones are zero in O; LSE does not
+     * depend on the mask.  p is dropout_p for a dense mask and floor(dropout_p * 65536) / 65536
+     * for the Philox mask.  Without active dropout the flag changes nothing. */
+    HK_FLAG_DROPOUT_SCALED = 1u << 6
 };
 
 /* ---- forward ------------------------------------------------------------

@@ -188,3 +188,102 @@ void hk_oracle_attn_backward(const float* Q, const float* K, const float* V, con
             }
         }
 }
+
+/* ---- inverted ("scaled") dropout -----------------------------------------
+ * The usual training-time definition, offered by the library as an option next
+ * to the reference's drop-then-renormalise one (the reference has no counterpart):
+ *   P = softmax(S) over ALL visible keys,   O_i = sum_j mask_ij * P_ij / (1-p) * v_j,
+ *   LSE_i = log sum_j exp(s_ij)   (independent of the mask).
+ * Backward: dPd_ij = mask_ij/(1-p) * dO_i.v_j,  D_i = dO_i.O_i,
+ *   dS = P * (dPd - D) * scale,  dV_j += mask_ij/(1-p) * P_ij * dO_i.
+ * `keep_scale` is 1/(1-p).  Pinned only by the finite-difference test. */
+void hk_oracle_attn_forward_scaled_dropout(const float* Q, const float* K, const float* V, int B, int H, int Tq, int Tk,
+                                           int Hd, float scale, int causal, int64_t q_pos0, int64_t k_pos0,
+                                           const float* mask, float keep_scale, float* O, float* LSE) {
+    for (int b = 0; b < B; ++b)
+        for (int h = 0; h < H; ++h) {
+            const int64_t bh = (int64_t)b * H + h;
+            const int64_t qbase = bh * Tq * Hd, kbase = bh * Tk * Hd, lbase = bh * Tq;
+            for (int i = 0; i < Tq; ++i) {
+                const float* qi = &Q[qbase + (int64_t)i * Hd];
+                int64_t jmax = Tk - 1;
+                if (causal) {
+                    int64_t lim = q_pos0 + i - k_pos0;
+                    if (lim < jmax) jmax = lim;
+                }
+                float m = -1e30f;
+                for (int64_t j = 0; j <= jmax; ++j) {
+                    const float* kj = &K[kbase + j * Hd];
+                    double d = 0;
+                    for (int k = 0; k < Hd; ++k) d += (double)qi[k] * kj[k];
+                    float s = (float)(d * scale);
+                    if (s > m) m = s;
+                }
+                double l = 0, oacc[HK_ORACLE_MAX_HD];
+                for (int k = 0; k < Hd; ++k) oacc[k] = 0;
+                for (int64_t j = 0; j <= jmax; ++j) {
+                    const float* kj = &K[kbase + j * Hd];
+                    const float* vj = &V[kbase + j * Hd];
+                    double d = 0;
+                    for (int k = 0; k < Hd; ++k) d += (double)qi[k] * kj[k];
+                    float e = expf((float)(d * scale) - m);
+                    l += e;
+                    const double w = (double)e * (mask ? mask[(bh * Tq + i) * (int64_t)Tk + j] * keep_scale : 1.0f);
+                    for (int k = 0; k < Hd; ++k) oacc[k] += w * vj[k];
+                }
+                double inv = (l > 0) ? 1.0 / l : 0.0;
+                for (int k = 0; k < Hd; ++k) O[qbase + (int64_t)i * Hd + k] = (float)(oacc[k] * inv);
+                LSE[lbase + i] = (l > 0) ? (float)(m + log(l)) : -INFINITY;
+            }
+        }
+}
+
+void hk_oracle_attn_backward_scaled_dropout(const float* Q, const float* K, const float* V, const float* O,
+                                            const float* dO, const float* LSE, int B, int H, int Tq, int Tk, int Hd,
+                                            float scale, int causal, int64_t q_pos0, int64_t k_pos0, const float* mask,
+                                            float keep_scale, float* D, float* dQ, float* dK, float* dV) {
+    memset(dQ, 0, sizeof(float) * (size_t)B * H * Tq * Hd);
+    memset(dK, 0, sizeof(float) * (size_t)B * H * Tk * Hd);
+    memset(dV, 0, sizeof(float) * (size_t)B * H * Tk * Hd);
+    for (int b = 0; b < B; ++b)
+        for (int h = 0; h < H; ++h) {
+            const int64_t bh = (int64_t)b * H + h;
+            const int64_t qbase = bh * Tq * Hd, kbase = bh * Tk * Hd, lbase = bh * Tq;
+            for (int i = 0; i < Tq; ++i) {
+                const float* qi = &Q[qbase + (int64_t)i * Hd];
+                const float* doi = &dO[qbase + (int64_t)i * Hd];
+                const float* oi = &O[qbase + (int64_t)i * Hd];
+                double Di = 0;
+                for (int k = 0; k < Hd; ++k) Di += (double)doi[k] * oi[k];
+                D[lbase + i] = (float)Di;
+                const float Li = LSE[lbase + i];
+                int64_t jmax = Tk - 1;
+                if (causal) {
+                    int64_t lim = q_pos0 + i - k_pos0;
+                    if (lim < jmax) jmax = lim;
+                }
+                float* dqi = &dQ[qbase + (int64_t)i * Hd];
+                if (Li == -INFINITY) continue;
+                for (int64_t j = 0; j <= jmax; ++j) {
+                    const float* kj = &K[kbase + j * Hd];
+                    const float* vj = &V[kbase + j * Hd];
+                    float* dkj = &dK[kbase + j * Hd];
+                    float* dvj = &dV[kbase + j * Hd];
+                    double sd = 0, dp = 0;
+                    for (int k = 0; k < Hd; ++k) {
+                        sd += (double)qi[k] * kj[k];
+                        dp += (double)doi[k] * vj[k];
+                    }
+                    const float w = mask ? mask[(bh * Tq + i) * (int64_t)Tk + j] * keep_scale : 1.0f;
+                    float p = expf((float)(sd * scale) - Li);
+                    float ds = (float)(p * (dp * w - Di) * scale);
+                    float pd = p * w;
+                    for (int k = 0; k < Hd; ++k) {
+                        dqi[k] += ds * kj[k];
+                        dkj[k] += ds * qi[k];
+                        dvj[k] += pd * doi[k];
+                    }
+                }
+            }
+        }
+}

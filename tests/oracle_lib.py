@@ -82,6 +82,35 @@ def attn_backward(Q, K, V, O, dO, LSE, scale, causal, mask=None, q_pos0=0, k_pos
     return D, dQ, dK, dV
 
 
+def attn_forward_scaled(Q, K, V, scale, causal, mask, p, q_pos0=0, k_pos0=0):
+    """Inverted dropout (mask / (1 - p), no renormalisation): see oracle/attn_oracle.c."""
+    B, H, Tq, Hd = Q.shape
+    Tk = K.shape[2]
+    Q, K, V = (np.ascontiguousarray(x, np.float32) for x in (Q, K, V))
+    O = np.empty((B, H, Tq, Hd), np.float32)
+    LSE = np.empty((B, H, Tq), np.float32)
+    mp = _p(np.ascontiguousarray(mask, np.float32)) if mask is not None else None
+    oracle().hk_oracle_attn_forward_scaled_dropout(_p(Q), _p(K), _p(V), B, H, Tq, Tk, Hd, C.c_float(scale), int(causal),
+                                                   C.c_int64(q_pos0), C.c_int64(k_pos0), mp,
+                                                   C.c_float(1.0 / (1.0 - p)), _p(O), _p(LSE))
+    return O, LSE
+
+
+def attn_backward_scaled(Q, K, V, O, dO, LSE, scale, causal, mask, p, q_pos0=0, k_pos0=0):
+    B, H, Tq, Hd = Q.shape
+    Tk = K.shape[2]
+    Q, K, V, O, dO, LSE = (np.ascontiguousarray(x, np.float32) for x in (Q, K, V, O, dO, LSE))
+    D = np.empty((B, H, Tq), np.float32)
+    dQ = np.empty((B, H, Tq, Hd), np.float32)
+    dK = np.empty((B, H, Tk, Hd), np.float32)
+    dV = np.empty((B, H, Tk, Hd), np.float32)
+    mp = _p(np.ascontiguousarray(mask, np.float32)) if mask is not None else None
+    oracle().hk_oracle_attn_backward_scaled_dropout(_p(Q), _p(K), _p(V), _p(O), _p(dO), _p(LSE), B, H, Tq, Tk, Hd,
+                                                    C.c_float(scale), int(causal), C.c_int64(q_pos0), C.c_int64(k_pos0),
+                                                    mp, C.c_float(1.0 / (1.0 - p)), _p(D), _p(dQ), _p(dK), _p(dV))
+    return D, dQ, dK, dV
+
+
 def precompute_D(dO, O):
     Hd = dO.shape[-1]
     dO, O = (np.ascontiguousarray(x, np.float32) for x in (dO, O))

@@ -317,6 +317,43 @@ def test_dropout_forward_backward(causal, mode):
     assert r is not None
 
 
+@pytest.mark.parametrize("causal", [0, 1])
+@pytest.mark.parametrize("mode", ["philox", "dense"])
+def test_inverted_dropout_forward_backward(causal, mode):
+    """HK_FLAG_DROPOUT_SCALED: normaliser over all visible keys, kept terms times 1/(1-p); no reference counterpart,
+    the oracle for it is pinned by finite differences (tests/test_oracle.py)."""
+    B, H, T, p, seed, off = 2, 2, 300, 0.1, 4242, 8
+    Q, K, V, dO = (normal((B, H, T, 64), 150 + s) for s in range(4))
+    mask = ol.dropout_mask(B * H, T, T, p, seed, off)
+    if mode == "philox":
+        kw = dict(dropout_p=p, philox_seed=seed, philox_offset=off, dropout_scaled=True)
+        p_eff = np.floor(p * 65536.0) / 65536.0  # the 16-bit threshold the mask was drawn with
+    else:
+        kw = dict(dropout_p=p, dropout_mask=dev(mask), dropout_scaled=True)
+        p_eff = p
+    O_ref, L_ref = ol.attn_forward_scaled(Q, K, V, SCALE, causal, mask, p_eff)
+    _, L_plain = ol.attn_forward(Q, K, V, SCALE, causal)
+    assert np.array_equal(L_ref, L_plain)
+    D_ref, dQ_ref, dK_ref, dV_ref = ol.attn_backward_scaled(Q, K, V, O_ref, dO, L_ref, SCALE, causal, mask, p_eff)
+    tQ, tK, tV, tdO = dev(Q), dev(K), dev(V), dev(dO)
+    O, LSE = hk.attention_forward(tQ, tK, tV, SCALE, causal, **kw)
+    ok_status()
+    gate("O", host(O), O_ref)
+    lse_check(host(LSE), L_ref)
+    for chained in (False, True):
+        Oin, Lin = (O, LSE) if chained else (dev(O_ref), dev(L_ref))
+        dQ, dK, dV, D = hk.attention_backward(tQ, tK, tV, Oin, tdO, Lin, SCALE, causal, **kw)
+        ok_status()
+        gate("D", host(D), D_ref, max_abs=2e-2 if chained else 1e-4, rel=1e-3 if chained else 1e-5)
+        gate("dQ", host(dQ), dQ_ref)
+        gate("dK", host(dK), dK_ref)
+        gate("dV", host(dV), dV_ref)
+    # the flag is inert without active dropout
+    O0, L0 = hk.attention_forward(tQ, tK, tV, SCALE, causal)
+    O1, L1 = hk.attention_forward(tQ, tK, tV, SCALE, causal, dropout_scaled=True)
+    assert torch.equal(O0, O1) and torch.equal(L0, L1)
+
+
 def test_fully_dropped_row():
     """Causal row 0 sees only key 0; when that key is dropped the reference gives O = 0, LSE = -inf
     (fused_attn_forward_kernel_tc_sm89.cu:412,424) and the backward must treat the row as p = 0."""

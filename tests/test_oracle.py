@@ -164,3 +164,33 @@ def test_oracle_shifted_window_equals_full():
     O, LSE = ol.attn_forward(Q, K, V, 0.125, 1)
     Ob, Lb = ol.attn_forward(Q[:, :, 16:32], K[:, :, :32], V[:, :, :32], 0.125, 1, q_pos0=16, k_pos0=0)
     assert np.array_equal(Ob, O[:, :, 16:32]) and np.array_equal(Lb, LSE[:, :, 16:32])
+
+
+def test_oracle_scaled_dropout_finite_difference():
+    """Inverted dropout (mask/(1-p), no renormalisation): float64 restatement + finite differences."""
+    rng = np.random.default_rng(8)
+    T, Hd, p = 9, 64, 0.3
+    Q, K, V, dO = (rng.standard_normal((1, 1, T, Hd)).astype(np.float32) for _ in range(4))
+    mask = ol.dropout_mask(1, T, T, p, seed=4, offset=0)
+    scale = 0.125
+
+    def f64(Qd):
+        S = (Qd[0, 0].astype(np.float64) @ K[0, 0].astype(np.float64).T) * scale
+        S = np.where(np.tril(np.ones((T, T), bool)), S, -np.inf)
+        P = np.exp(S - S.max(-1, keepdims=True))
+        P = P / P.sum(-1, keepdims=True)
+        return float((((P * mask[0] / (1 - p)) @ V[0, 0].astype(np.float64)) * dO[0, 0]).sum())
+
+    O, LSE = ol.attn_forward_scaled(Q, K, V, scale, 1, mask, p)
+    O0, LSE0 = ol.attn_forward(Q, K, V, scale, 1)
+    assert np.array_equal(LSE, LSE0)  # the mask does not enter the normaliser
+    _, dQ, _, _ = ol.attn_backward_scaled(Q, K, V, O, dO, LSE, scale, 1, mask, p)
+    eps = 1e-3
+    for (i, k) in [(0, 0), (3, 5), (8, 63)]:
+        Qp = Q.astype(np.float64).copy(); Qm = Qp.copy()
+        Qp[0, 0, i, k] += eps; Qm[0, 0, i, k] -= eps
+        fd = (f64(Qp) - f64(Qm)) / (2 * eps)
+        assert abs(fd - dQ[0, 0, i, k]) < 2e-4 * max(1.0, abs(fd)), (i, k, fd, dQ[0, 0, i, k])
+    # without a mask it is the plain attention
+    O1, _ = ol.attn_forward_scaled(Q, K, V, scale, 1, None, 0.0)
+    assert np.allclose(O1, O0, atol=1e-7)
