@@ -57,6 +57,7 @@ struct __align__(16) Shared {
     float lse[2][TILE];   // LSE * log2e of the query tile (+inf for rows past the end), double-buffered
     float dsum[2][TILE];  // D * scale of the query tile
     uint64_t kv_full, qk_full, qk_empty, qm_full, qm_free, s_full, p_ready, b_done, ds_ready, dq_full, dq_empty, staged;
+    uint64_t dq_staged[2];  // dQ of query tile i sits in staging buffer i & 1, ready for the bulk reduction
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -83,7 +84,7 @@ __device__ __forceinline__ void stamp(const BwdArgs& a, bool on, int it, int rol
 
 enum WaitId {
     W_KVFULL = 201, W_QKFULL, W_QKEMPTY, W_QMFULL, W_QMFREE, W_SFULL, W_PREADY, W_BDONE, W_DSREADY, W_DQFULL, W_DQEMPTY,
-    W_STAGED
+    W_STAGED, W_DQSTAGED
 };
 
 }  // namespace bwd
@@ -92,7 +93,8 @@ __global__ void __launch_bounds__(bwd::NUM_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapdO,
                 const __grid_constant__ CUtensorMap mapQm, const __grid_constant__ CUtensorMap mapKm,
-                const __grid_constant__ CUtensorMap mapdOm, const BwdArgs a) {
+                const __grid_constant__ CUtensorMap mapdOm, const __grid_constant__ CUtensorMap mapdQ,
+                const BwdArgs a) {
     using namespace bwd;
     extern __shared__ __align__(1024) uint8_t smem[];
     if ((smem_u32(smem) & 1023u) != 0) {  // never expected; refuse to run on a misplaced buffer
@@ -141,6 +143,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         mbar_init(&sh.dq_full, 1);
         mbar_init(&sh.dq_empty, 256);  // the two column groups that drain dQ
         mbar_init(&sh.staged, 256);    // the threads that stage LSE and D
+        mbar_init(&sh.dq_staged[0], 256);
+        mbar_init(&sh.dq_staged[1], 256);
         sh.abort_flag = 0;
         fence_mbar_init();
     }
@@ -166,6 +170,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tma_prefetch_desc(&mapQm);
             tma_prefetch_desc(&mapKm);
             tma_prefetch_desc(&mapdOm);
+            tma_prefetch_desc(&mapdQ);
             mbar_arrive_expect_tx(&sh.kv_full, 3 * TILE_BYTES);
             tma_load_4d(sK, &mapK, &sh.kv_full, 0, kv0, h, b);
             tma_load_4d(sK + BOX_BYTES, &mapK, &sh.kv_full, HALF_D, kv0, h, b);
@@ -190,17 +195,37 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qm_full, HALF_D, q0, h, b);
                 ++issued_m;
             };
+            // dQ of query tile j, staged by the compute warps in buffer j & 1 (the K-major Q or dO tile, idle
+            // between S^T/dP^T of one query tile and the prefetch of the next): add it to global memory
+            auto reduce_dq = [&](int j) -> bool {
+                if (!mbar_wait(wc, &sh.dq_staged[j & 1], (j >> 1) & 1, W_DQSTAGED, j)) return false;
+                const uint8_t* src = (j & 1) ? sdO : sQ;
+                const int q = (it0 + j) * TILE;
+                tma_reduce_add_4d(&mapdQ, src, 0, q, h, b);
+                tma_reduce_add_4d(&mapdQ, src + BOX_BYTES, HALF_D, q, h, b);
+                bulk_commit_group();
+                return true;
+            };
+            bool tok = true;
             load_qk(it0 * TILE);
             load_qm(it0 * TILE);
             for (int it = 0; it + 1 < n_it; ++it) {
                 const int q1 = (it0 + it + 1) * TILE;
-                // K-major Q, dO: free as soon as S^T(it), dP^T(it) are done
-                if (!mbar_wait(wc, &sh.qk_empty, it & 1, W_QKEMPTY, it)) break;
+                // K-major Q, dO: free as soon as S^T(it), dP^T(it) are done ...
+                if (!(tok = mbar_wait(wc, &sh.qk_empty, it & 1, W_QKEMPTY, it))) break;
+                // ... but dQ(it-1) passes through one of them first
+                if (it > 0) {
+                    if (!(tok = reduce_dq(it - 1))) break;
+                    bulk_wait_group_read_all();
+                }
                 load_qk(q1);
                 // MN-major Q, dO double as the dS staging area: free once dQ(it) is done
-                if (!mbar_wait(wc, &sh.qm_free, it & 1, W_QMFREE, it)) break;
+                if (!(tok = mbar_wait(wc, &sh.qm_free, it & 1, W_QMFREE, it))) break;
                 load_qm(q1);
             }
+            if (tok && n_it >= 2) tok = reduce_dq(n_it - 2);
+            if (tok) tok = reduce_dq(n_it - 1);
+            bulk_wait_group_all();
             // Do not leave the CTA while bulk copies into its shared memory are in flight.
             for (int i = 0; i < 100000 && !mbar_try_wait(&sh.kv_full, 0); ++i) {}
             if (issued_k > 0)
@@ -286,10 +311,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
         const float* lse_bh = a.LSE + (int64_t)b * a.lse_sB + (int64_t)h * a.lse_sH;
         const float* d_bh = a.D + (int64_t)b * a.d_sB + (int64_t)h * a.d_sH;
-        float* dq_bh = a.dQ + (int64_t)b * a.dq_sB + (int64_t)h * a.dq_sH;
         bool ok = true;
         uint32_t rs[32], rp[32];
         const bool tlc = tl && tid == 0;
+        // dQ of query tile j (this thread: query row `row`, columns 32*part..) into staging buffer j & 1 in the
+        // layout of a 128-byte-swizzled TMA box: 16-byte chunk c of row r at chunk position c ^ (r & 7).
+        // The buffer is free: dq_full(j) implies that S^T/dP^T of tile j+1, its last readers, are complete,
+        // and the producer refills it only after the reduction has read it.
+        auto stage_dq = [&](int j, const uint32_t* v) {
+            uint8_t* srow = ((j & 1) ? sdO : sQ) + part * BOX_BYTES + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) =
+                    make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+            fence_proxy_async_smem();
+            mbar_arrive(&sh.dq_staged[j & 1]);
+        };
 
         for (int it = 0; it < n_it; ++it) {
             const int q0 = (it0 + it) * TILE;
@@ -449,18 +486,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (it - 1) & 1, W_DQFULL, it - 1));
                 if (!ok) break;
                 tc_fence_after_sync();
-                const int q = q0 - TILE + row;
-                float* dq_row = dq_bh + (int64_t)q * a.dq_sM + part * 32;
                 tmem_ld32(trow + COL_DQ + part * 32, rs);
                 tmem_wait_ld();
                 tc_fence_before_sync();
                 mbar_arrive(&sh.dq_empty);  // dQ is in registers: the next dQ = dS K may overwrite tensor memory
-                if (q < a.Tq) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        red_add_v4(dq_row + i, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]),
-                                   __uint_as_float(rs[i + 2]), __uint_as_float(rs[i + 3]));
-                }
+                stage_dq(it - 1, rs);
             }
 
             // dS into shared memory (MN-major A operand of dQ = dS K), over the MN-major Q/dO copies once dV/dK
@@ -470,11 +500,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             if (!ok) break;
             stamp(a, tlc, it, 1, 6);
             {
+                // Rows r and r + 4 share a 32-byte chunk position; they store its two halves in opposite order so
+                // that the eight lanes of a quarter-warp hit eight different 16-byte bank groups.
                 uint8_t* drow = sdS + part * BOX_BYTES + row * 128;
+                const bool swap = (row >> 2) & 1;
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
-                    uint4 v = make_uint4(rp[4 * t], rp[4 * t + 1], rp[4 * t + 2], rp[4 * t + 3]);
-                    *reinterpret_cast<uint4*>(drow + ((((t >> 1) ^ (row & 3)) << 5) | ((t & 1) << 4))) = v;
+                for (int u = 0; u < 4; ++u) {
+                    const uint4 lo = make_uint4(rp[8 * u], rp[8 * u + 1], rp[8 * u + 2], rp[8 * u + 3]);
+                    const uint4 hi = make_uint4(rp[8 * u + 4], rp[8 * u + 5], rp[8 * u + 6], rp[8 * u + 7]);
+                    uint8_t* chunk = drow + ((u ^ (row & 3)) << 5);
+                    *reinterpret_cast<uint4*>(chunk + (swap ? 16 : 0)) = swap ? hi : lo;
+                    *reinterpret_cast<uint4*>(chunk + (swap ? 0 : 16)) = swap ? lo : hi;
                 }
             }
             fence_proxy_async_smem();
@@ -487,16 +523,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (n_it - 1) & 1, W_DQFULL, n_it - 1));
             if (ok) {
                 tc_fence_after_sync();
-                const int q = (it0 + n_it - 1) * TILE + row;
-                float* dq_row = dq_bh + (int64_t)q * a.dq_sM + part * 32;
                 tmem_ld32(trow + COL_DQ + part * 32, rs);
                 tmem_wait_ld();
-                if (q < a.Tq) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        red_add_v4(dq_row + i, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]),
-                                   __uint_as_float(rs[i + 2]), __uint_as_float(rs[i + 3]));
-                }
+                stage_dq(n_it - 1, rs);
             }
         }
 
@@ -558,7 +587,7 @@ int launch_attn_bwd(const BwdMaps& m, const BwdArgs& a, cudaStream_t stream) {
     if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
     timing_mark(TIMED_BWD, true, stream);
     attn_bwd_kernel<<<(unsigned)nblocks, bwd::NUM_THREADS, bwd::SMEM_BYTES, stream>>>(m.q, m.k, m.v, m.dO, m.q_mn, m.k_mn,
-                                                                                       m.dO_mn, a);
+                                                                                       m.dO_mn, m.dQ, a);
     timing_mark(TIMED_BWD, false, stream);
     count_launch();
     return check_launch();

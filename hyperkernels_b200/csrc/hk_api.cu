@@ -402,6 +402,8 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     if ((rc = make_tile_map(&m.q_mn, tQ.ptr, HEAD_DIM, B, H, Tq, tQ.sB, tQ.sM, tQ.sH, TILE, true))) return rc;
     if ((rc = make_tile_map(&m.k_mn, tK.ptr, HEAD_DIM, B, H, Tk, tK.sB, tK.sM, tK.sH, TILE, true))) return rc;
     if ((rc = make_tile_map(&m.dO_mn, tdO.ptr, HEAD_DIM, B, H, Tq, tdO.sB, tdO.sM, tdO.sH, TILE, true))) return rc;
+    if ((rc = make_tile_map(&m.dQ, p->dQ, HEAD_DIM, B, H, Tq, p->dq_strideB, p->dq_strideM, p->dq_strideH, TILE, false)))
+        return rc;
     if (!d_given) {
         DJob j{};
         j.dO = vdO; j.O = vO;
