@@ -56,8 +56,8 @@ constexpr int COL_DQ = 384;
 struct __align__(16) Shared {
     float lse[2][TILE];   // LSE * log2e of the query tile (+inf for rows past the end), double-buffered
     float dsum[2][TILE];  // D * scale of the query tile
-    uint64_t kv_full, qk_full, qk_empty, qm_full, qm_free, s_full, p_ready, b_done, ds_ready, dq_full, dq_empty, staged;
-    uint64_t dq_staged[2];  // dQ of query tile i sits in staging buffer i & 1, ready for the bulk reduction
+    uint64_t k_full, v_full, km_full, q_full, do_full, qk_empty, qm_full, qm_free, s_full, p_ready, b_done, ds_ready, dq_full, dq_empty, staged;
+    uint64_t dq_staged[2];  // dQ of a query tile is staged for the bulk reduction ([1]: the last tile, other buffer)
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -131,8 +131,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const int n_it = n_qtiles - it0;
 
     if (threadIdx.x == 0) {
-        mbar_init(&sh.kv_full, 1);
-        mbar_init(&sh.qk_full, 1);
+        mbar_init(&sh.k_full, 1);
+        mbar_init(&sh.v_full, 1);
+        mbar_init(&sh.km_full, 1);
+        mbar_init(&sh.q_full, 1);
+        mbar_init(&sh.do_full, 1);
         mbar_init(&sh.qk_empty, 1);
         mbar_init(&sh.qm_full, 1);
         mbar_init(&sh.qm_free, 1);
@@ -171,21 +174,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tma_prefetch_desc(&mapKm);
             tma_prefetch_desc(&mapdOm);
             tma_prefetch_desc(&mapdQ);
-            mbar_arrive_expect_tx(&sh.kv_full, 3 * TILE_BYTES);
-            tma_load_4d(sK, &mapK, &sh.kv_full, 0, kv0, h, b);
-            tma_load_4d(sK + BOX_BYTES, &mapK, &sh.kv_full, HALF_D, kv0, h, b);
-            tma_load_4d(sV, &mapV, &sh.kv_full, 0, kv0, h, b);
-            tma_load_4d(sV + BOX_BYTES, &mapV, &sh.kv_full, HALF_D, kv0, h, b);
-            tma_load_4d(sKm, &mapKm, &sh.kv_full, 0, kv0, h, b);
-            tma_load_4d(sKm + BOX_BYTES, &mapKm, &sh.kv_full, HALF_D, kv0, h, b);
-            int issued_k = 0, issued_m = 0;
-            auto load_qk = [&](int q0) {
-                mbar_arrive_expect_tx(&sh.qk_full, 2 * TILE_BYTES);
-                tma_load_4d(sQ, &mapQ, &sh.qk_full, 0, q0, h, b);
-                tma_load_4d(sQ + BOX_BYTES, &mapQ, &sh.qk_full, HALF_D, q0, h, b);
-                tma_load_4d(sdO, &mapdO, &sh.qk_full, 0, q0, h, b);
-                tma_load_4d(sdO + BOX_BYTES, &mapdO, &sh.qk_full, HALF_D, q0, h, b);
-                ++issued_k;
+            // in the order the first products need them: K, Q (S^T), V, dO (dP^T), the MN-major Q, dO (dV, dK), K (dQ)
+            int issued_q = 0, issued_do = 0, issued_m = 0;
+            auto load_q = [&](int q0) {
+                mbar_arrive_expect_tx(&sh.q_full, TILE_BYTES);
+                tma_load_4d(sQ, &mapQ, &sh.q_full, 0, q0, h, b);
+                tma_load_4d(sQ + BOX_BYTES, &mapQ, &sh.q_full, HALF_D, q0, h, b);
+                ++issued_q;
+            };
+            auto load_do = [&](int q0) {
+                mbar_arrive_expect_tx(&sh.do_full, TILE_BYTES);
+                tma_load_4d(sdO, &mapdO, &sh.do_full, 0, q0, h, b);
+                tma_load_4d(sdO + BOX_BYTES, &mapdO, &sh.do_full, HALF_D, q0, h, b);
+                ++issued_do;
             };
             auto load_qm = [&](int q0) {
                 mbar_arrive_expect_tx(&sh.qm_full, 2 * TILE_BYTES);
@@ -195,30 +196,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qm_full, HALF_D, q0, h, b);
                 ++issued_m;
             };
-            // dQ of query tile j, staged by the compute warps in buffer j & 1 (the K-major Q or dO tile, idle
-            // between S^T/dP^T of one query tile and the prefetch of the next): add it to global memory
+            // dQ of query tile j, staged by the compute warps in the K-major dO tile (the K-major Q tile for the
+            // last one), which is idle between dP^T of one query tile and the prefetch of the next: add it to
+            // global memory
             auto reduce_dq = [&](int j) -> bool {
-                if (!mbar_wait(wc, &sh.dq_staged[j & 1], (j >> 1) & 1, W_DQSTAGED, j)) return false;
-                const uint8_t* src = (j & 1) ? sdO : sQ;
+                const int last = (j == n_it - 1) ? 1 : 0;
+                if (!mbar_wait(wc, &sh.dq_staged[last], last ? 0 : (j & 1), W_DQSTAGED, j)) return false;
+                const uint8_t* src = last ? sQ : sdO;
                 const int q = (it0 + j) * TILE;
                 tma_reduce_add_4d(&mapdQ, src, 0, q, h, b);
                 tma_reduce_add_4d(&mapdQ, src + BOX_BYTES, HALF_D, q, h, b);
                 bulk_commit_group();
                 return true;
             };
-            bool tok = true;
-            load_qk(it0 * TILE);
+            mbar_arrive_expect_tx(&sh.k_full, TILE_BYTES);
+            tma_load_4d(sK, &mapK, &sh.k_full, 0, kv0, h, b);
+            tma_load_4d(sK + BOX_BYTES, &mapK, &sh.k_full, HALF_D, kv0, h, b);
+            load_q(it0 * TILE);
+            mbar_arrive_expect_tx(&sh.v_full, TILE_BYTES);
+            tma_load_4d(sV, &mapV, &sh.v_full, 0, kv0, h, b);
+            tma_load_4d(sV + BOX_BYTES, &mapV, &sh.v_full, HALF_D, kv0, h, b);
+            load_do(it0 * TILE);
             load_qm(it0 * TILE);
+            mbar_arrive_expect_tx(&sh.km_full, TILE_BYTES);
+            tma_load_4d(sKm, &mapKm, &sh.km_full, 0, kv0, h, b);
+            tma_load_4d(sKm + BOX_BYTES, &mapKm, &sh.km_full, HALF_D, kv0, h, b);
+            bool tok = true;
             for (int it = 0; it + 1 < n_it; ++it) {
                 const int q1 = (it0 + it + 1) * TILE;
                 // K-major Q, dO: free as soon as S^T(it), dP^T(it) are done ...
                 if (!(tok = mbar_wait(wc, &sh.qk_empty, it & 1, W_QKEMPTY, it))) break;
-                // ... but dQ(it-1) passes through one of them first
+                load_q(q1);
+                // ... but dQ(it-1) passes through the dO tile first
                 if (it > 0) {
                     if (!(tok = reduce_dq(it - 1))) break;
                     bulk_wait_group_read_all();
                 }
-                load_qk(q1);
+                load_do(q1);
                 // MN-major Q, dO double as the dS staging area: free once dQ(it) is done
                 if (!(tok = mbar_wait(wc, &sh.qm_free, it & 1, W_QMFREE, it))) break;
                 load_qm(q1);
@@ -227,11 +241,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             if (tok) tok = reduce_dq(n_it - 1);
             bulk_wait_group_all();
             // Do not leave the CTA while bulk copies into its shared memory are in flight.
-            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.kv_full, 0); ++i) {}
-            if (issued_k > 0)
-                for (int i = 0; i < 100000 && !mbar_try_wait(&sh.qk_full, (issued_k - 1) & 1); ++i) {}
-            if (issued_m > 0)
-                for (int i = 0; i < 100000 && !mbar_try_wait(&sh.qm_full, (issued_m - 1) & 1); ++i) {}
+            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.k_full, 0); ++i) {}
+            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.v_full, 0); ++i) {}
+            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.km_full, 0); ++i) {}
+            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.q_full, (issued_q - 1) & 1); ++i) {}
+            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.do_full, (issued_do - 1) & 1); ++i) {}
+            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.qm_full, (issued_m - 1) & 1); ++i) {}
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
@@ -242,24 +257,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             const uint32_t k_addr = smem_u32(sK), km_addr = smem_u32(sKm), v_addr = smem_u32(sV), q_addr = smem_u32(sQ),
                            do_addr = smem_u32(sdO), qm_addr = smem_u32(sQm), dom_addr = smem_u32(sdOm),
                            ds_addr = smem_u32(sdS);
-            auto issue_a = [&]() {
+            // S^T and dP^T of query tile `it` (local index), each as soon as its own operands have landed
+            auto issue_a = [&](int it) -> bool {
+                if (it == 0 && !mbar_wait(wc, &sh.k_full, 0, W_KVFULL, 0)) return false;
+                if (!mbar_wait(wc, &sh.q_full, it & 1, W_QKFULL, it)) return false;
+                tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // S^T = K Q^T
                     umma_ss_tf32(tmem + COL_S, kmajor_desc(k_addr, kk, BOX_BYTES), kmajor_desc(q_addr, kk, BOX_BYTES),
                                  IDESC_ST, kk > 0);
+                if (it == 0 && !mbar_wait(wc, &sh.v_full, 0, W_KVFULL, 1)) return false;
+                if (!mbar_wait(wc, &sh.do_full, it & 1, W_QKFULL, 1000 + it)) return false;
+                tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // dP^T = V dO^T
                     umma_ss_tf32(tmem + COL_DP, kmajor_desc(v_addr, kk, BOX_BYTES), kmajor_desc(do_addr, kk, BOX_BYTES),
                                  IDESC_ST, kk > 0);
                 umma_commit(&sh.s_full);
                 umma_commit(&sh.qk_empty);
+                return true;
             };
-            bool ok = mbar_wait(wc, &sh.kv_full, 0, W_KVFULL);
-            if (ok) ok = mbar_wait(wc, &sh.qk_full, 0, W_QKFULL, 0);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_a();
-            }
+            bool ok = issue_a(0);
             for (int it = 0; ok && it < n_it; ++it) {
                 const uint32_t par = it & 1;
                 stamp(a, tl, it, 0, 0);
@@ -279,15 +297,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 stamp(a, tl, it, 0, 2);
                 if (it + 1 < n_it) {
                     // next tile's S^T, dP^T: P^T and dS^T of this tile were consumed by the MMAs just issued
-                    if (!(ok = mbar_wait(wc, &sh.qk_full, (it + 1) & 1, W_QKFULL, it + 1))) break;
                     stamp(a, tl, it, 0, 3);
-                    tc_fence_after_sync();
-                    issue_a();
+                    if (!(ok = issue_a(it + 1))) break;
                     stamp(a, tl, it, 0, 4);
                 }
                 if (!(ok = mbar_wait(wc, &sh.ds_ready, par, W_DSREADY, it))) break;
                 stamp(a, tl, it, 0, 5);
                 if (it > 0 && !(ok = mbar_wait(wc, &sh.dq_empty, (it - 1) & 1, W_DQEMPTY, it))) break;
+                if (it == 0 && !(ok = mbar_wait(wc, &sh.km_full, 0, W_KVFULL, 2))) break;
                 stamp(a, tl, it, 0, 6);
                 tc_fence_after_sync();
 #pragma unroll
@@ -314,18 +331,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         bool ok = true;
         uint32_t rs[32], rp[32];
         const bool tlc = tl && tid == 0;
-        // dQ of query tile j (this thread: query row `row`, columns 32*part..) into staging buffer j & 1 in the
+        // dQ of query tile j (this thread: query row `row`, columns 32*part..) into the staging buffer in the
         // layout of a 128-byte-swizzled TMA box: 16-byte chunk c of row r at chunk position c ^ (r & 7).
         // The buffer is free: dq_full(j) implies that S^T/dP^T of tile j+1, its last readers, are complete,
         // and the producer refills it only after the reduction has read it.
         auto stage_dq = [&](int j, const uint32_t* v) {
-            uint8_t* srow = ((j & 1) ? sdO : sQ) + part * BOX_BYTES + row * 128;
+            const int last = (j == n_it - 1) ? 1 : 0;
+            uint8_t* srow = (last ? sQ : sdO) + part * BOX_BYTES + row * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) =
                     make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
             fence_proxy_async_smem();
-            mbar_arrive(&sh.dq_staged[j & 1]);
+            mbar_arrive(&sh.dq_staged[last]);
         };
 
         for (int it = 0; it < n_it; ++it) {
