@@ -56,7 +56,7 @@ constexpr int COL_DQ = 384;
 struct __align__(16) Shared {
     float lse[2][TILE];   // LSE * log2e of the query tile (+inf for rows past the end), double-buffered
     float dsum[2][TILE];  // D * scale of the query tile
-    uint64_t k_full, v_full, km_full, q_full, do_full, qk_empty, qm_full, qm_free, s_full, p_ready, b_done, ds_ready, dq_full, dq_empty, staged;
+    uint64_t k_full, v_full, km_full, q_full, do_full, qk_empty, qm_full, qm_free, s_full, dp_full, p_ready, b_done, ds_ready, dq_full, dq_empty, staged;
     uint64_t dq_staged[2];  // dQ of a query tile is staged for the bulk reduction ([1]: the last tile, other buffer)
     uint32_t tmem_base;
     int abort_flag;
@@ -97,6 +97,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 const BwdArgs a) {
     using namespace bwd;
     extern __shared__ __align__(1024) uint8_t smem[];
+    // schedule trace (timeline_block < 0): {start ns, end ns, SM id, query tiles} of each of the first 1024 CTAs
+    const bool trace = a.timeline != nullptr && a.timeline_block < 0 && blockIdx.x < 1024 && threadIdx.x == 0;
+    if (trace) {
+        a.timeline[4 * blockIdx.x] = (long long)globaltimer_ns();
+        a.timeline[4 * blockIdx.x + 2] = smid();
+    }
     if ((smem_u32(smem) & 1023u) != 0) {  // never expected; refuse to run on a misplaced buffer
         if (threadIdx.x == 0 && atomicCAS(&a.status->code, 0, 299) == 0) a.status->block = blockIdx.x;
         return;
@@ -140,6 +146,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         mbar_init(&sh.qm_full, 1);
         mbar_init(&sh.qm_free, 1);
         mbar_init(&sh.s_full, 1);
+        mbar_init(&sh.dp_full, 1);
         mbar_init(&sh.p_ready, NUM_COMPUTE);
         mbar_init(&sh.b_done, 1);
         mbar_init(&sh.ds_ready, NUM_COMPUTE);
@@ -160,7 +167,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem = sh.tmem_base;
     WaitCtx wc{&sh.abort_flag, a.status};
-    const bool tl = a.timeline != nullptr && (int)blockIdx.x == a.timeline_block;
+    const bool tl = a.timeline != nullptr && (int)blockIdx.x == a.timeline_block;  // never in trace mode
     if (tl && threadIdx.x == 0) a.timeline[0] = n_it;
 
     if (warp == 0) {
@@ -266,6 +273,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // S^T = K Q^T
                     umma_ss_tf32(tmem + COL_S, kmajor_desc(k_addr, kk, BOX_BYTES), kmajor_desc(q_addr, kk, BOX_BYTES),
                                  IDESC_ST, kk > 0);
+                umma_commit(&sh.s_full);  // the exponentials need S^T only
                 if (it == 0 && !mbar_wait(wc, &sh.v_full, 0, W_KVFULL, 1)) return false;
                 if (!mbar_wait(wc, &sh.do_full, it & 1, W_QKFULL, 1000 + it)) return false;
                 tc_fence_after_sync();
@@ -273,7 +281,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // dP^T = V dO^T
                     umma_ss_tf32(tmem + COL_DP, kmajor_desc(v_addr, kk, BOX_BYTES), kmajor_desc(do_addr, kk, BOX_BYTES),
                                  IDESC_ST, kk > 0);
-                umma_commit(&sh.s_full);
+                umma_commit(&sh.dp_full);
                 umma_commit(&sh.qk_empty);
                 return true;
             };
@@ -346,6 +354,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             mbar_arrive(&sh.dq_staged[last]);
         };
 
+        // LSE * log2e (threads 0..127; +inf past the end and for a fully dropped row, so that every p is 0) or
+        // D * scale (threads 128..255) of query row q0 + (tid & 127)
+        auto fetch_lse_or_d = [&](int q0) -> float {
+            const int q = q0 + (tid & 127);
+            if (tid < TILE) {
+                if (q >= a.Tq) return INFINITY;
+                const float l = __ldg(lse_bh + q);
+                return (l == -INFINITY) ? INFINITY : l * LOG2E;
+            }
+            return (q < a.Tq) ? __ldg(d_bh + q) * a.scale : 0.f;
+        };
+        float staged_val = (tid < 2 * TILE && n_it > 0) ? fetch_lse_or_d(it0 * TILE) : 0.f;
+
         for (int it = 0; it < n_it; ++it) {
             const int q0 = (it0 + it) * TILE;
             stamp(a, tlc, it, 1, 0);
@@ -353,19 +374,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             // The buffer was last read two tiles ago; every compute thread passed that tile's ds_ready
             // arrival long before this thread could get here (it has since waited on dq_full or s_full
             // of the previous tile, which follow it).
+            // The value was fetched from global memory one tile ahead, so that its latency is not paid here.
             if (tid < 2 * TILE) {
-                const int q = q0 + (tid & 127);
-                if (tid < TILE) {
-                    float L = INFINITY;
-                    if (q < a.Tq) {
-                        const float l = __ldg(lse_bh + q);
-                        L = (l == -INFINITY) ? INFINITY : l * LOG2E;  // fully dropped row: every p is 0
-                    }
-                    sh.lse[it & 1][tid] = L;
-                } else {
-                    sh.dsum[it & 1][tid - TILE] = (q < a.Tq) ? __ldg(d_bh + q) * a.scale : 0.f;
-                }
+                if (tid < TILE)
+                    sh.lse[it & 1][tid] = staged_val;
+                else
+                    sh.dsum[it & 1][tid - TILE] = staged_val;
                 mbar_arrive(&sh.staged);
+                if (it + 1 < n_it) staged_val = fetch_lse_or_d(q0 + TILE);
             }
             // an mbarrier rather than bar.sync: its wait is bounded, so a CTA that is
             // winding down after a failed wait cannot strand warps at a barrier
@@ -378,7 +394,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tc_fence_after_sync();
 
             tmem_ld32(trow + COL_S + c0, rs);
-            tmem_ld32(trow + COL_DP + c0, rp);
 
             // first query column (local to the tile) this key row is visible to
             int cmin = 0;
@@ -428,66 +443,63 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 if (lo > 0) vis = (lo >= 32) ? 0u : (0xffffffffu << lo);
                 keep &= vis;
             }
+            // pairs whose p is zero: hidden ones, and dropped ones unless the dropout is the inverted kind
+            const uint32_t live = a.drop_scaled ? vis : keep;
+            tmem_wait_ld();
+
+            // p = exp2(s*scale*log2e - LSE*log2e) needs S^T only: dP^T is still being computed
+            {
+                const float4* lse4 = reinterpret_cast<const float4*>(sh.lse[it & 1] + c0);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const float4 L = lse4[g];
+                    const float Ls[4] = {L.x, L.y, L.z, L.w};
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const int i = g * 4 + t;
+                        rs[i] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -Ls[t])));
+                    }
+                }
+                if (live != 0xffffffffu) {  // tiles on the diagonal, the ragged end, dropout
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (!((live >> i) & 1u)) rs[i] = 0u;
+                }
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dp_full, it & 1, W_SFULL, 1000 + it));
+            if (!ok) break;
+            tc_fence_after_sync();
+            tmem_ld32(trow + COL_DP + c0, rp);
             tmem_wait_ld();
             stamp(a, tlc, it, 1, 3);
 
-            // p = exp2(s*scale*log2e - LSE*log2e);  dS = p * (dP*scale - D*scale)
-            const float4* lse4 = reinterpret_cast<const float4*>(sh.lse[it & 1] + c0);
-            const float4* ds4 = reinterpret_cast<const float4*>(sh.dsum[it & 1] + c0);
-            if (keep == 0xffffffffu) {
-                // every pair visible and kept: no per-element integer work besides the two roundings
+            // dS = p * (dP*scale - D*scale)
+            {
+                const float4* ds4 = reinterpret_cast<const float4*>(sh.dsum[it & 1] + c0);
+                const bool dropped_some = a.drop_scaled && keep != 0xffffffffu;
+                if (dropped_some) {
+                    // inverted dropout: a dropped pair keeps the -D term of dS but contributes neither dP (zeroed
+                    // here) nor to dV (its P^T entry is zeroed below, after dS has been formed)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (!((keep >> i) & 1u)) rp[i] = 0u;
+                }
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
-                    const float4 L = lse4[g];
                     const float4 Dv = ds4[g];
-                    const float Ls[4] = {L.x, L.y, L.z, L.w};
                     const float Ds[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
                         const int i = g * 4 + t;
-                        const float p = ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -Ls[t]));
-                        const float ds = p * fmaf(__uint_as_float(rp[i]), a.dp_scale, -Ds[t]);
-                        rs[i] = tf32_round_bits_mma(__float_as_uint(p));
+                        const float ds = __uint_as_float(rs[i]) * fmaf(__uint_as_float(rp[i]), a.dp_scale, -Ds[t]);
+                        rs[i] = tf32_round_bits_mma(rs[i]);
                         rp[i] = tf32_round_bits_mma(__float_as_uint(ds));
                     }
                 }
-            } else if (a.drop_scaled) {
-                // inverted dropout: p is the softmax over all visible keys; a dropped pair keeps the -D term of
-                // dS but contributes neither dP nor to dV
+                if (dropped_some) {
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float4 L = lse4[g];
-                    const float4 Dv = ds4[g];
-                    const float Ls[4] = {L.x, L.y, L.z, L.w};
-                    const float Ds[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        const int i = g * 4 + t;
-                        float p = ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -Ls[t]));
-                        if (!((vis >> i) & 1u)) p = 0.f;
-                        const bool kept = (keep >> i) & 1u;
-                        const float dp = kept ? __uint_as_float(rp[i]) : 0.f;
-                        const float ds = p * fmaf(dp, a.dp_scale, -Ds[t]);
-                        rs[i] = kept ? tf32_round_bits_mma(__float_as_uint(p)) : 0u;
-                        rp[i] = tf32_round_bits_mma(__float_as_uint(ds));
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const float4 L = lse4[g];
-                    const float4 Dv = ds4[g];
-                    const float Ls[4] = {L.x, L.y, L.z, L.w};
-                    const float Ds[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        const int i = g * 4 + t;
-                        float p = ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -Ls[t]));
-                        if (!((keep >> i) & 1u)) p = 0.f;
-                        const float ds = p * fmaf(__uint_as_float(rp[i]), a.scale, -Ds[t]);
-                        rs[i] = tf32_round_bits_mma(__float_as_uint(p));
-                        rp[i] = tf32_round_bits_mma(__float_as_uint(ds));
-                    }
+                    for (int i = 0; i < 32; ++i)
+                        if (!((keep >> i) & 1u)) rs[i] = 0u;
                 }
             }
             stamp(a, tlc, it, 1, 4);
@@ -588,6 +600,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem, TMEM_COLS);
+    }
+    if (trace) {
+        a.timeline[4 * blockIdx.x + 1] = (long long)globaltimer_ns();
+        a.timeline[4 * blockIdx.x + 3] = n_it;
     }
 }
 
