@@ -57,6 +57,7 @@ struct __align__(16) Shared {
     float lse[2][TILE];   // LSE * log2e of the query tile (+inf for rows past the end), double-buffered
     float dsum[2][TILE];  // D * scale of the query tile
     uint64_t k_full, v_full, km_full, q_full, do_full, qk_empty, qm_full, qm_free, s_full, dp_full, p_ready, b_done, ds_ready, dq_full, dq_empty, staged;
+    uint64_t acc_staged;    // dV, dK of the CTA are staged for the bulk store
     uint64_t dq_staged[2];  // dQ of a query tile is staged for the bulk reduction ([1]: the last tile, other buffer)
     uint32_t tmem_base;
     int abort_flag;
@@ -84,7 +85,7 @@ __device__ __forceinline__ void stamp(const BwdArgs& a, bool on, int it, int rol
 
 enum WaitId {
     W_KVFULL = 201, W_QKFULL, W_QKEMPTY, W_QMFULL, W_QMFREE, W_SFULL, W_PREADY, W_BDONE, W_DSREADY, W_DQFULL, W_DQEMPTY,
-    W_STAGED, W_DQSTAGED
+    W_STAGED, W_DQSTAGED, W_ACCSTAGED
 };
 
 }  // namespace bwd
@@ -94,6 +95,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapdO,
                 const __grid_constant__ CUtensorMap mapQm, const __grid_constant__ CUtensorMap mapKm,
                 const __grid_constant__ CUtensorMap mapdOm, const __grid_constant__ CUtensorMap mapdQ,
+                const __grid_constant__ CUtensorMap mapdK, const __grid_constant__ CUtensorMap mapdV,
                 const BwdArgs a) {
     using namespace bwd;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -153,6 +155,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         mbar_init(&sh.dq_full, 1);
         mbar_init(&sh.dq_empty, 256);  // the two column groups that drain dQ
         mbar_init(&sh.staged, 256);    // the threads that stage LSE and D
+        mbar_init(&sh.acc_staged, NUM_COMPUTE);
         mbar_init(&sh.dq_staged[0], 256);
         mbar_init(&sh.dq_staged[1], 256);
         sh.abort_flag = 0;
@@ -181,6 +184,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tma_prefetch_desc(&mapKm);
             tma_prefetch_desc(&mapdOm);
             tma_prefetch_desc(&mapdQ);
+            tma_prefetch_desc(&mapdK);
+            tma_prefetch_desc(&mapdV);
             // in the order the first products need them: K, Q (S^T), V, dO (dP^T), the MN-major Q, dO (dV, dK), K (dQ)
             int issued_q = 0, issued_do = 0, issued_m = 0;
             auto load_q = [&](int q0) {
@@ -245,6 +250,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 load_qm(q1);
             }
             if (tok && n_it >= 2) tok = reduce_dq(n_it - 2);
+            // dV and dK, staged by the compute warps in the K-major V and K tiles (dead after the last S^T, dP^T):
+            // stored -- added, if the caller accumulates -- with bulk copies; a thread-per-row store would be
+            // 32 lines per instruction
+            if (tok && (tok = mbar_wait(wc, &sh.acc_staged, 0, W_ACCSTAGED, 0))) {
+                if (a.accum_dkdv) {
+                    tma_reduce_add_4d(&mapdV, sV, 0, kv0, h, b);
+                    tma_reduce_add_4d(&mapdV, sV + BOX_BYTES, HALF_D, kv0, h, b);
+                    tma_reduce_add_4d(&mapdK, sK, 0, kv0, h, b);
+                    tma_reduce_add_4d(&mapdK, sK + BOX_BYTES, HALF_D, kv0, h, b);
+                } else {
+                    tma_store_4d(&mapdV, sV, 0, kv0, h, b);
+                    tma_store_4d(&mapdV, sV + BOX_BYTES, HALF_D, kv0, h, b);
+                    tma_store_4d(&mapdK, sK, 0, kv0, h, b);
+                    tma_store_4d(&mapdK, sK + BOX_BYTES, HALF_D, kv0, h, b);
+                }
+                bulk_commit_group();
+            }
             if (tok) tok = reduce_dq(n_it - 1);
             bulk_wait_group_all();
             // Do not leave the CTA while bulk copies into its shared memory are in flight.
@@ -548,6 +570,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             stamp(a, tlc, it, 1, 7);
         }
 
+        // dV and dK of this KV tile are complete (b_done of the last query tile covered every product into them).
+        // Column groups 0,1 put dV (times 1/(1-p) for inverted dropout) and groups 2,3 dK into the K-major V and K
+        // buffers, as the boxes of a 128-byte-swizzled TMA tile: 16-byte chunk c of row r at position c ^ (r & 7).
+        if (ok && n_it > 0) {
+            tc_fence_after_sync();
+            tmem_ld32(trow + ((part < 2) ? COL_DV + part * 32 : COL_DK + (part - 2) * 32), rs);
+            tmem_wait_ld();
+            const float f = (part < 2) ? a.dv_scale : 1.f;
+            uint8_t* srow = ((part < 2) ? sV : sK) + (part & 1) * BOX_BYTES + row * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<float4*>(srow + ((c ^ (row & 7)) << 4)) =
+                    make_float4(__uint_as_float(rs[4 * c]) * f, __uint_as_float(rs[4 * c + 1]) * f,
+                                __uint_as_float(rs[4 * c + 2]) * f, __uint_as_float(rs[4 * c + 3]) * f);
+            fence_proxy_async_smem();
+            mbar_arrive(&sh.acc_staged);
+        } else if (n_it == 0 && kv_ok && !a.accum_dkdv) {
+            // no query sees this KV tile: its dK and dV rows are zero
+            float* out_row = (part < 2)
+                                 ? a.dV + (int64_t)b * a.dv_sB + (int64_t)h * a.dv_sH + (int64_t)kvrow * a.dv_sM + part * 32
+                                 : a.dK + (int64_t)b * a.dk_sB + (int64_t)h * a.dk_sH + (int64_t)kvrow * a.dk_sM + (part - 2) * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(out_row + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+
         // dQ of the last query tile
         if (ok && n_it > 0 && part < 2) {
             ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (n_it - 1) & 1, W_DQFULL, n_it - 1));
@@ -556,39 +603,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tmem_ld32(trow + COL_DQ + part * 32, rs);
                 tmem_wait_ld();
                 stage_dq(n_it - 1, rs);
-            }
-        }
-
-        // epilogue: dV and dK of this KV tile.  The last dq_full covered every MMA issued; column groups 2 and 3
-        // did not wait on it in the loop, so everybody waits here.  Groups 0,1 store dV, groups 2,3 store dK.
-        if (ok && n_it > 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (n_it - 1) & 1, W_DQFULL, n_it));
-        tc_fence_after_sync();
-        float* out_row = (part < 2)
-                             ? a.dV + (int64_t)b * a.dv_sB + (int64_t)h * a.dv_sH + (int64_t)kvrow * a.dv_sM + part * 32
-                             : a.dK + (int64_t)b * a.dk_sB + (int64_t)h * a.dk_sH + (int64_t)kvrow * a.dk_sM + (part - 2) * 32;
-        const int col = (part < 2) ? COL_DV + part * 32 : COL_DK + (part - 2) * 32;
-        if (ok && n_it > 0) {
-            tmem_ld32(trow + col, rs);
-            tmem_wait_ld();
-            if (part < 2 && a.dv_scale != 1.f) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) rs[i] = __float_as_uint(__uint_as_float(rs[i]) * a.dv_scale);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) rs[i] = 0u;
-        }
-        if (kv_ok) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-                float4 v = make_float4(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1]), __uint_as_float(rs[i + 2]),
-                                       __uint_as_float(rs[i + 3]));
-                float4* d4 = reinterpret_cast<float4*>(out_row + i);
-                if (a.accum_dkdv) {
-                    const float4 o = *d4;
-                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *d4 = v;
             }
         }
     }
@@ -621,7 +635,7 @@ int launch_attn_bwd(const BwdMaps& m, const BwdArgs& a, cudaStream_t stream) {
     if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
     timing_mark(TIMED_BWD, true, stream);
     attn_bwd_kernel<<<(unsigned)nblocks, bwd::NUM_THREADS, bwd::SMEM_BYTES, stream>>>(m.q, m.k, m.v, m.dO, m.q_mn, m.k_mn,
-                                                                                       m.dO_mn, m.dQ, a);
+                                                                                       m.dO_mn, m.dQ, m.dK, m.dV, a);
     timing_mark(TIMED_BWD, false, stream);
     count_launch();
     return check_launch();

@@ -56,10 +56,11 @@ struct BwdArgs {
 };
 
 // K-major maps (16-byte-chunk swizzle) of Q, K, V, dO and MN-major maps
-// (32-byte-chunk swizzle) of Q, K, dO over the same memory; dQ is the
-// destination of the kernel's bulk reductions (16-byte-chunk swizzle).
+// (32-byte-chunk swizzle) of Q, K, dO over the same memory; dQ, dK, dV are
+// the destinations of the kernel's bulk reductions and stores (16-byte-chunk
+// swizzle).
 struct BwdMaps {
-    CUtensorMap q, k, v, dO, q_mn, k_mn, dO_mn, dQ;
+    CUtensorMap q, k, v, dO, q_mn, k_mn, dO_mn, dQ, dK, dV;
 };
 
 int launch_attn_bwd(const BwdMaps& m, const BwdArgs& a, cudaStream_t stream);

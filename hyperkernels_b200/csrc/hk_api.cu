@@ -404,6 +404,10 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     if ((rc = make_tile_map(&m.dO_mn, tdO.ptr, HEAD_DIM, B, H, Tq, tdO.sB, tdO.sM, tdO.sH, TILE, true))) return rc;
     if ((rc = make_tile_map(&m.dQ, p->dQ, HEAD_DIM, B, H, Tq, p->dq_strideB, p->dq_strideM, p->dq_strideH, TILE, false)))
         return rc;
+    if ((rc = make_tile_map(&m.dK, p->dK, HEAD_DIM, B, H, Tk, p->dk_strideB, p->dk_strideM, p->dk_strideH, TILE, false)))
+        return rc;
+    if ((rc = make_tile_map(&m.dV, p->dV, HEAD_DIM, B, H, Tk, p->dv_strideB, p->dv_strideM, p->dv_strideH, TILE, false)))
+        return rc;
     if (!d_given) {
         DJob j{};
         j.dO = vdO; j.O = vO;

@@ -147,6 +147,13 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// Requests the tile into L2 only (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+
 // 4-D tile reduction, shared -> global: global[tile] += shared tile (fp32 add performed by the
 // memory system).  Rows of the box that lie outside the tensor are skipped.  Completion is tracked
 // by the issuing thread's bulk async-group.  The shared-memory tile must have been written, and
@@ -156,6 +163,13 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const 
     asm volatile(
         "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group"
         " [%0, {%2, %3, %4, %5}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+// 4-D tile store, shared -> global; same rules as the reduction above.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
         ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
