@@ -82,7 +82,7 @@ __device__ __forceinline__ int kv_tiles_for(const FwdArgs& a, int q0) {
 
 __global__ void __launch_bounds__(fwd::NUM_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                const __grid_constant__ CUtensorMap mapV, const FwdArgs a) {
+                const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, const FwdArgs a) {
     using namespace fwd;
     extern __shared__ __align__(1024) uint8_t smem[];
     if ((smem_u32(smem) & 1023u) != 0) {  // never expected; refuse to run on a misplaced buffer
@@ -395,8 +395,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 64; ++i) r[i] = 0u;
         }
-        if (row_ok) {
-            float* orow = a.O + (int64_t)b * a.o_sB + (int64_t)h * a.o_sH + (int64_t)qrow * a.o_sM;
+        // O leaves through shared memory and a TMA bulk store (a thread-per-row store would touch 32 lines per
+        // instruction).  The tile's own Q buffer is dead -- o_full covered its last S = Q K^T -- and takes the
+        // two 32-column boxes of a 128-byte-swizzled TMA tile: 16-byte chunk c of row r at position c ^ (r & 7).
+        // Rows past the end of the sequence are clipped by the copy.
+        // (a tile that had no key tile to wait for must still let the load of its Q land before reusing the buffer)
+        if (nt == 0 && n > 0) __all_sync(0xffffffffu, mbar_wait(wc, &sh.q_full, 0, W_QFULL, 0));
+        {
+            uint8_t* srow = sQ + t * TILE_BYTES + row * 128;
 #pragma unroll
             for (int i = 0; i < 64; i += 4) {
                 float4 v;
@@ -404,17 +410,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 v.y = __uint_as_float(r[i + 1]) * inv_l;
                 v.z = __uint_as_float(r[i + 2]) * inv_l;
                 v.w = __uint_as_float(r[i + 3]) * inv_l;
-                *reinterpret_cast<float4*>(orow + i) = v;
+                const int c = (i >> 2) & 7;
+                *reinterpret_cast<float4*>(srow + (i >> 5) * BOX_BYTES + ((c ^ (row & 7)) << 4)) = v;
             }
+            fence_proxy_async_smem();
+        }
+        if (row_ok)
             a.LSE[(int64_t)b * a.lse_sB + (int64_t)h * a.lse_sH + qrow] = (l > 0.f) ? (m + log2f(l)) * LN2 : -INFINITY;
+        // the 128 threads of this query tile (every one gets here, whatever `ok` is), then one of them stores
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");
+        if (row == 0 && q0 + t * TILE < a.Tq) {
+            tma_store_4d(&mapO, sQ + t * TILE_BYTES, 0, q0 + t * TILE, h, b);
+            tma_store_4d(&mapO, sQ + t * TILE_BYTES + BOX_BYTES, HALF_D, q0 + t * TILE, h, b);
+            bulk_commit_group();
+            bulk_wait_group_all();
         }
         tc_fence_before_sync();
         __syncthreads();  // pairs with the control warps' barrier before tensor memory is freed
     }
 }
 
-int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdArgs& a,
-                    cudaStream_t stream) {
+int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                    const FwdArgs& a, cudaStream_t stream) {
     static bool attr_done[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return HK_ERR_CUDA;
@@ -427,7 +444,7 @@ int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     const long long nblocks = (long long)a.n_qtiles * a.BH;
     if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
     timing_mark(TIMED_FWD, true, stream);
-    attn_fwd_kernel<<<(unsigned)nblocks, fwd::NUM_THREADS, fwd::SMEM_BYTES, stream>>>(mq, mk, mv, a);
+    attn_fwd_kernel<<<(unsigned)nblocks, fwd::NUM_THREADS, fwd::SMEM_BYTES, stream>>>(mq, mk, mv, mo, a);
     timing_mark(TIMED_FWD, false, stream);
     count_launch();
     return check_launch();

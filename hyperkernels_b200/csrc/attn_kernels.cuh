@@ -25,8 +25,9 @@ struct FwdArgs {
     int timeline_block;
 };
 
-int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdArgs& a,
-                    cudaStream_t stream);
+// mq, mk, mv: TMA maps of the (rounded) operands; mo: map of O, the destination of the kernel's bulk stores.
+int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                    const FwdArgs& a, cudaStream_t stream);
 
 struct BwdArgs {
     const float* LSE;

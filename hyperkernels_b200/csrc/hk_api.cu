@@ -304,7 +304,9 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     if (!a.status) return HK_ERR_CUDA;
     a.timeline = g_timeline;
     a.timeline_block = g_timeline_block;
-    return launch_attn_fwd(mq, mk, mv, a, stream);
+    CUtensorMap mo;
+    if ((rc = make_tile_map(&mo, p->O, HEAD_DIM, B, H, Tq, p->o_strideB, p->o_strideM, p->o_strideH, TILE))) return rc;
+    return launch_attn_fwd(mq, mk, mv, mo, a, stream);
 }
 
 int hk_attn_bwd_precompute_D(const hk_attn_bwd_params* p, void* stream_) {
