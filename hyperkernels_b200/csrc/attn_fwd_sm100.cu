@@ -85,6 +85,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, const FwdArgs a) {
     using namespace fwd;
     extern __shared__ __align__(1024) uint8_t smem[];
+    // schedule trace (timeline_block < 0): {start ns, end ns, SM id, key tiles} of each of the first 1024 CTAs
+    const bool trace = a.timeline != nullptr && a.timeline_block < 0 && blockIdx.x < 1024 && threadIdx.x == 0;
+    if (trace) {
+        a.timeline[4 * blockIdx.x] = (long long)globaltimer_ns();
+        a.timeline[4 * blockIdx.x + 2] = smid();
+    }
     if ((smem_u32(smem) & 1023u) != 0) {  // never expected; refuse to run on a misplaced buffer
         if (threadIdx.x == 0 && atomicCAS(&a.status->code, 0, 199) == 0) a.status->block = blockIdx.x;
         return;
@@ -427,6 +433,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
         tc_fence_before_sync();
         __syncthreads();  // pairs with the control warps' barrier before tensor memory is freed
+    }
+    if (trace) {
+        a.timeline[4 * blockIdx.x + 1] = (long long)globaltimer_ns();
+        a.timeline[4 * blockIdx.x + 3] = n;
     }
 }
 

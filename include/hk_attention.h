@@ -240,7 +240,7 @@ int hk_attn_selftest(int which, const float* A, const float* B, float* out, void
 /* Performance debugging: while `device_buffer` (device memory, 4096 int64) is set, CTA
  * number `block` of every forward/backward launch writes SM-clock stamps of its
  * pipeline phases into it (slot layout in csrc/attn_*_sm100.cu).  With block = -1 every
- * CTA b < 1024 of a backward launch instead writes {start ns, end ns, SM id, query tiles}
+ * CTA b < 1024 of a forward or backward launch instead writes {start ns, end ns, SM id, tiles}
  * to slots 4b..4b+3 (the schedule of the launch).  NULL turns it off.
  * No counterpart in the reference. */
 void hk_attn_debug_timeline(long long* device_buffer, int block);
