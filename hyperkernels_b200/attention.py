@@ -117,6 +117,7 @@ def lib() -> C.CDLL:
         L.hk_attn_forward.argtypes = [C.POINTER(MemEfficientFwdParams), C.c_void_p]
         L.hk_attn_backward.argtypes = [C.POINTER(MemEfficientBwdParams), C.c_void_p]
         L.hk_attn_bwd_precompute_D.argtypes = [C.POINTER(MemEfficientBwdParams), C.c_void_p]
+        L.hk_attn_bwd_precompute_D_hd.argtypes = [C.POINTER(MemEfficientBwdParams), C.c_int, C.c_void_p]
         L.hk_attn_fwd_workspace_bytes.restype = C.c_size_t
         L.hk_attn_fwd_workspace_bytes.argtypes = [C.POINTER(MemEfficientFwdParams)]
         L.hk_attn_bwd_workspace_bytes.restype = C.c_size_t
@@ -153,9 +154,14 @@ def fused_attn_forward(params: MemEfficientFwdParams, stream=None) -> None:
     _check(lib().hk_attn_forward(C.byref(params), _stream_handle(stream)), "hk_attn_forward")
 
 
-def mem_efficient_bwd_precompute_D(params: MemEfficientBwdParams, stream=None) -> None:
-    """mem_efficient_bwd_precompute_D_sm89<64><<<...>>>(params) -> hk_attn_bwd_precompute_D."""
-    _check(lib().hk_attn_bwd_precompute_D(C.byref(params), _stream_handle(stream)), "hk_attn_bwd_precompute_D")
+def mem_efficient_bwd_precompute_D(params: MemEfficientBwdParams, stream=None, head_dim: int = 64) -> None:
+    """mem_efficient_bwd_precompute_D_sm89<head_dim><<<...>>>(params) -> hk_attn_bwd_precompute_D[_hd];
+    head_dim is the reference's template argument (16, 32, 64, 128 or 256)."""
+    if head_dim == 64:
+        _check(lib().hk_attn_bwd_precompute_D(C.byref(params), _stream_handle(stream)), "hk_attn_bwd_precompute_D")
+    else:
+        _check(lib().hk_attn_bwd_precompute_D_hd(C.byref(params), int(head_dim), _stream_handle(stream)),
+               "hk_attn_bwd_precompute_D_hd")
 
 
 def mem_efficient_bwd_unified(params: MemEfficientBwdParams, stream=None) -> None:

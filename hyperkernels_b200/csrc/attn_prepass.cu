@@ -107,6 +107,60 @@ int launch_precompute_D(const DJob& j, cudaStream_t stream) {
 }
 
 // ---------------------------------------------------------------------------
+// The same row sum for the other head dimensions the reference instantiates
+// (mem_efficient_bwd_precompute_D_sm89.cu:93-102: 16 ... 256): HD/4 lanes per
+// row (at most a warp; two float4 per lane for 256), shuffle reduction.
+// ---------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(256) precompute_D_hd_kernel(const DJob j) {
+    constexpr int LANES = (HD / 4 < 32) ? HD / 4 : 32;  // lanes that share a row
+    constexpr int VEC = HD / 4 / LANES;                  // float4 per lane
+    const long long nrows = (long long)j.BH * j.T;
+    const int sub = threadIdx.x % LANES;
+    const long long stride = ((long long)gridDim.x * blockDim.x) / LANES;
+    const long long rows_pad = (nrows + 32 / LANES - 1) / (32 / LANES) * (32 / LANES);  // whole warps iterate together
+    for (long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES; row < rows_pad; row += stride) {
+        float s = 0.f;
+        int b = 0, h = 0, r = 0;
+        if (row < nrows) {
+            const int bh = (int)(row / j.T);
+            r = (int)(row - (long long)bh * j.T);
+            b = bh / j.H;
+            h = bh - b * j.H;
+            const float4* g4 = reinterpret_cast<const float4*>(j.dO.ptr + (int64_t)b * j.dO.sB + (int64_t)h * j.dO.sH +
+                                                               (int64_t)r * j.dO.sM);
+            const float4* o4 = reinterpret_cast<const float4*>(j.O.ptr + (int64_t)b * j.O.sB + (int64_t)h * j.O.sH +
+                                                               (int64_t)r * j.O.sM);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                const float4 g = __ldg(g4 + sub + v * LANES), o = __ldg(o4 + sub + v * LANES);
+                s += g.x * o.x + g.y * o.y + g.z * o.z + g.w * o.w;
+            }
+        }
+#pragma unroll
+        for (int off = LANES / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (row < nrows && sub == 0) j.D[(int64_t)b * j.d_sB + (int64_t)h * j.d_sH + r] = s;
+    }
+}
+
+int launch_precompute_D_hd(const DJob& j, int head_dim, cudaStream_t stream) {
+    const long long nrows = (long long)j.BH * j.T;
+    if (nrows == 0) return HK_OK;
+    const int lanes = head_dim / 4 < 32 ? head_dim / 4 : 32;
+    const int blocks = (int)std::min<long long>((nrows * lanes + 255) / 256, 148 * 8);
+    switch (head_dim) {
+        case 16: precompute_D_hd_kernel<16><<<blocks, 256, 0, stream>>>(j); break;
+        case 32: precompute_D_hd_kernel<32><<<blocks, 256, 0, stream>>>(j); break;
+        case 64: precompute_D_hd_kernel<64><<<blocks, 256, 0, stream>>>(j); break;
+        case 128: precompute_D_hd_kernel<128><<<blocks, 256, 0, stream>>>(j); break;
+        case 256: precompute_D_hd_kernel<256><<<blocks, 256, 0, stream>>>(j); break;
+        default: return HK_ERR_UNSUPPORTED;
+    }
+    count_launch();
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------
 // zero a strided [B, H, T, 64] tensor (dQ is accumulated with atomics; the
 // reference leaves this to its caller, kernels_test.cu:562)
 // ---------------------------------------------------------------------------

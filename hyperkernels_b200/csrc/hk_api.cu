@@ -328,6 +328,25 @@ int hk_attn_bwd_precompute_D(const hk_attn_bwd_params* p, void* stream_) {
     return launch_precompute_D(j, stream);
 }
 
+int hk_attn_bwd_precompute_D_hd(const hk_attn_bwd_params* p, int head_dim, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (!p) return HK_ERR_NULL_POINTER;
+    if (!p->dO || !p->O || !p->D) return HK_ERR_NULL_POINTER;
+    if (p->B <= 0 || p->nh <= 0 || p->T <= 0) return HK_ERR_BAD_SHAPE;
+    if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256) return HK_ERR_UNSUPPORTED;
+    if (!aligned16(p->dO) || !aligned16(p->O)) return HK_ERR_MISALIGNED;
+    const int64_t st[] = {p->o_strideB, p->o_strideM, p->o_strideH, p->do_strideB, p->do_strideM, p->do_strideH};
+    for (int64_t s : st)
+        if (!stride_ok(s)) return HK_ERR_MISALIGNED;
+    if (p->o_strideM < head_dim || p->do_strideM < head_dim) return HK_ERR_BAD_SHAPE;
+    DJob j{};
+    j.dO = View4{p->dO, p->do_strideB, p->do_strideM, p->do_strideH};
+    j.O = View4{p->O, p->o_strideB, p->o_strideM, p->o_strideH};
+    j.D = p->D; j.d_sB = p->d_strideB; j.d_sH = p->d_strideH;
+    j.H = p->nh; j.BH = p->B * p->nh; j.T = p->T;
+    return launch_precompute_D_hd(j, head_dim, stream);
+}
+
 int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!p) return HK_ERR_NULL_POINTER;

@@ -180,6 +180,12 @@ int hk_attn_forward_static_scratch(const hk_attn_fwd_params* p, void* stream);
  * Reads dO, O and their strides, B, nh, T; writes D. */
 int hk_attn_bwd_precompute_D(const hk_attn_bwd_params* p, void* stream);
 
+/* The same pre-pass for the other head dimensions the reference instantiates it for
+ * (mem_efficient_bwd_precompute_D_sm89<16|32|64|128|256>,
+ * kernels/attention/mem_efficient_bwd_precompute_D_sm89.cu:93-102): dO and O rows hold
+ * `head_dim` floats.  The attention kernels themselves are head_dim 64 only. */
+int hk_attn_bwd_precompute_D_hd(const hk_attn_bwd_params* p, int head_dim, void* stream);
+
 /* Replaces the launch of OwnTensor::mem_efficient_bwd_unified_kernel_exp12<64,Causal>
  * (kernels/tests/kernels_test.cu:562-584; kernel at
  * kernels/attention/mem_efficient_bwd_unified_kernel_exp12.cu:54-329) together

@@ -261,6 +261,31 @@ def test_strided_bthd_layout_prerounded():
     gate("dQ", host(dQ), dQ_ref); gate("dK", host(dK), dK_ref); gate("dV", host(dV), dV_ref)
 
 
+def test_packed_qkv_layout():
+    """Packed [B, T, 3, H, 64] storage (the output of a fused QKV projection): Q, K, V are views into one buffer,
+    addressed through the reference block's stride triplets (fused_attn_forward_kernel_tc_sm89.cu:24-28); the
+    gradients go into a buffer of the same packing.  Arbitrary fp32 inputs: the rounding pre-pass reads the strided
+    views."""
+    B, H, T = 2, 4, 333
+    qkv = normal((B, T, 3, H, 64), 35)
+    dO = normal((B, H, T, 64), 36)
+    Q, K, V = (np.ascontiguousarray(qkv[:, :, i].transpose(0, 2, 1, 3)) for i in range(3))
+    O_ref, L_ref = ol.attn_forward_mt(Q, K, V, SCALE, 1)
+    D_ref, dQ_ref, dK_ref, dV_ref = ol.attn_backward_mt(Q, K, V, O_ref, dO, L_ref, SCALE, 1)
+    t_qkv = dev(qkv)
+    tQ, tK, tV = (t_qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    assert tQ.stride() == (T * 3 * H * 64, 64, 3 * H * 64, 1)
+    O, LSE = hk.attention_forward(tQ, tK, tV, SCALE, 1)
+    ok_status()
+    gate("O", host(O), O_ref)
+    lse_check(host(LSE), L_ref)
+    t_grad = torch.full((B, T, 3, H, 64), float("nan"), device="cuda")
+    gQ, gK, gV = (t_grad[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    hk.attention_backward(tQ, tK, tV, O, dev(dO), LSE, SCALE, 1, dQ=gQ, dK=gK, dV=gV)
+    ok_status()
+    gate("dQ", host(gQ), dQ_ref); gate("dK", host(gK), dK_ref); gate("dV", host(gV), dV_ref)
+
+
 def test_negative_scale_and_large_scores():
     """Every 64th key row scaled x8 (the long-sequence config's stress of the running max), and a negative scale."""
     Q, K, V, dO = (normal((1, 2, 512, 64), 40 + s) for s in range(4))
@@ -388,6 +413,30 @@ def test_precompute_D_reference_shape():
     hk.mem_efficient_bwd_precompute_D(p)
     ok_status()
     assert ol.max_abs(host(D), ol.precompute_D(dO, O)) <= 1e-4
+
+
+@pytest.mark.parametrize("hd", [16, 32, 64, 128, 256])
+def test_precompute_D_other_head_dims(hd):
+    """mem_efficient_bwd_precompute_D_sm89.cu:93-102 instantiates the pre-pass for these head dimensions; rows of a
+    [B, T, H, hd] layout (strided heads) and a ragged row count."""
+    B, H, T = 2, 3, 517
+    rng = np.random.default_rng(hd)
+    dO = rng.standard_normal((B, T, H, hd)).astype(np.float32)
+    O = rng.standard_normal((B, T, H, hd)).astype(np.float32)
+    tdO, tO = dev(dO), dev(O)
+    D = torch.empty((B, H, T), device="cuda")
+    p = hk.MemEfficientBwdParams()
+    p.dO, p.O, p.D = tdO.data_ptr(), tO.data_ptr(), D.data_ptr()
+    p.B, p.nh, p.T, p.scale = B, H, T, 1.0
+    p.do_strideB, p.do_strideM, p.do_strideH = T * H * hd, H * hd, hd
+    p.o_strideB, p.o_strideM, p.o_strideH = T * H * hd, H * hd, hd
+    p.d_strideB, p.d_strideH = H * T, T
+    hk.mem_efficient_bwd_precompute_D(p, head_dim=hd)
+    ok_status()
+    ref = (dO.astype(np.float64) * O).sum(-1).transpose(0, 2, 1)
+    assert np.abs(host(D) - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
+    with pytest.raises(hk.HKError):
+        hk.mem_efficient_bwd_precompute_D(p, head_dim=48)
 
 
 def test_backward_with_precomputed_D_and_accumulation():
