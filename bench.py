@@ -40,7 +40,7 @@ CONFIGS = {
 METRIC = "attn fwd+bwd TF32 TFLOP/s"
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the backward kernel at the bench
 # workload (see profiles/); None until a capture exists for that config.
-NCU_TRAFFIC_BYTES = {2: 183.6e6}  # profiles/attn_bwd_kernel_cfg2.md: 141.6 MB read + 42.0 MB written
+NCU_TRAFFIC_BYTES = {2: 191.8e6}  # profiles/attn_bwd_kernel_cfg2.md: 145.5 MB read + 46.3 MB written
 
 
 def flops(cfg, heads=None, fwd=True, bwd=True):
