@@ -29,4 +29,6 @@ from .attention import (  # noqa: F401
     FLAG_ACCUM_DQ,
     FLAG_D_PRECOMPUTED,
     FLAG_REUSE_FWD_ROUNDED,
+    FLAG_DROPOUT_SCALED,
 )
+from .host_step import HostAttentionStep  # noqa: F401

@@ -470,6 +470,30 @@ def test_backward_reuses_forward_rounded_operands():
     assert torch.equal(dK, dK2) and torch.equal(dV, dV2)
 
 
+@pytest.mark.parametrize("chunks", [1, 2, 4])
+def test_host_step_pipeline_matches_direct_calls(chunks):
+    """HostAttentionStep (pinned host tensors, batch chunks, copies overlapped with kernels) gives what the direct
+    device-tensor calls give: O, LSE, dK, dV bit for bit (each (b,h) slice is computed the same way), dQ up to the
+    order of its fp32 reductions."""
+    B, H, T = 4, 3, 384
+    Q, K, V, dO = (normal((B, H, T, 64), 80 + s) for s in range(4))
+    tQ, tK, tV, tdO = dev(Q), dev(K), dev(V), dev(dO)
+    O, LSE = hk.attention_forward(tQ, tK, tV, SCALE, 1)
+    dQ, dK, dV, _ = hk.attention_backward(tQ, tK, tV, O, tdO, LSE, SCALE, 1)
+    hin = [torch.from_numpy(x).pin_memory() for x in (Q, K, V, dO)]
+    hO, hdQ, hdK, hdV = (torch.full((B, H, T, 64), float("nan")).pin_memory() for _ in range(4))
+    hLSE = torch.full((B, H, T), float("nan")).pin_memory()
+    hs = hk.HostAttentionStep(B, H, T, SCALE, True, chunks=chunks)
+    for _ in range(2):  # the second step reuses every buffer slot
+        hs.step(*hin, hO, hLSE, hdQ, hdK, hdV)
+        torch.cuda.synchronize()
+    ok_status()
+    assert torch.equal(hO, O.cpu()) and torch.equal(hLSE, LSE.cpu())
+    assert torch.equal(hdK, dK.cpu()) and torch.equal(hdV, dV.cpu())
+    assert float((hdQ - dQ.cpu()).abs().max()) <= 1e-4
+    assert hs.h2d_bytes == 4 * Q.nbytes and hs.d2h_bytes == 4 * Q.nbytes + LSE.numel() * 4
+
+
 def test_merge_partial_equals_full():
     """Keys split into two blocks, each attended separately, merged: equals attention over all keys."""
     B, H, Tq, Tk = 2, 2, 200, 384
