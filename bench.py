@@ -341,7 +341,7 @@ def run_ours(args, cfg, rank, local_rank, world):
                          "peak_source": peaks["source"], "traffic": NCU_TRAFFIC_BYTES.get(args.config)},
             "e2e": {"value": total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
-                    "call": "hyperkernels_b200.HostAttentionStep.step: pinned host tensors in and out, %d batch chunks, "
+                    "call": "hyperkernels_b200.HostAttentionStep.step: pinned host tensors in and out, %d chunks of (batch, head) slices, "
                             "H2D / kernels / D2H of different chunks overlapped on three streams" % host_step.chunks,
                     "sequential": {"value": total / (ms_e2e_seq * 1e-3) / 1e12, "ms_per_step": ms_e2e_seq,
                                    "call": "copy in, hk_attn_forward + hk_attn_backward, copy out on one stream"}},

@@ -8,7 +8,10 @@ step, which at these sizes is an order of magnitude more than the kernels.  The
 (batch, head) slices of the problem are independent, so this helper cuts the
 batch into chunks and runs three queues: chunk i+1 travels to the device while
 the kernels work on chunk i and the results of chunk i-1 travel back (the two
-copy directions use different DMA engines and the link is full duplex).
+copy directions use different DMA engines and the link is full duplex).  The
+chunks are runs of consecutive (batch, head) slices, so a single-batch problem
+with many heads is pipelined too; small problems (under 2 MB per tensor and
+chunk) are not cut, the extra launches would cost more than the overlap gains.
 
 Everything on the device goes through the C ABI (``hk_attn_forward`` and
 ``hk_attn_backward`` per chunk, with preallocated buffers and workspace); torch
@@ -38,19 +41,20 @@ class HostAttentionStep:
 
         self.torch = torch
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        n = B * H  # independent slices; a chunk is a run of them, handed to the kernels as a batch of one-head items
         if chunks is None:
-            chunks = next(c for c in (4, 2, 1) if B % c == 0)
-        if B % chunks != 0:
-            raise ValueError("the batch must divide into equal chunks")
+            chunks = next(c for c in (4, 2, 1) if n % c == 0 and (c == 1 or n // c * T * 256 >= (2 << 20)))
+        if n % chunks != 0:
+            raise ValueError("batch x heads must divide into equal chunks")
         self.B, self.H, self.T, self.scale, self.causal = B, H, T, float(scale), bool(causal)
-        self.chunks, self.cb = chunks, B // chunks
+        self.chunks, self.cb = chunks, n // chunks
         self.drop = {}
         if dropout_p > 0:
             if philox_seed is None:
                 raise ValueError("dropout on this path uses the Philox mask: give philox_seed")
             self.drop = dict(dropout_p=dropout_p, philox_seed=philox_seed)
         self.philox_offset = philox_offset
-        shp, lshp = (self.cb, H, T, 64), (self.cb, H, T)
+        shp, lshp = (self.cb, 1, T, 64), (self.cb, 1, T)
         n_slots = min(2, chunks)
         self.slots = []
         for _ in range(n_slots):
@@ -58,7 +62,7 @@ class HostAttentionStep:
                  for k in ("Q", "K", "V", "dO", "O", "dQ", "dK", "dV")}
             s["LSE"] = torch.empty(lshp, dtype=torch.float32, device=self.device)
             s["D"] = torch.empty(lshp, dtype=torch.float32, device=self.device)
-            s["ws"] = torch.empty(4 * self.cb * H * T * 256 + 512, dtype=torch.uint8, device=self.device)
+            s["ws"] = torch.empty(4 * self.cb * T * 256 + 512, dtype=torch.uint8, device=self.device)
             self.slots.append(s)
         self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(device=self.device) for _ in range(3))
         self.ev_start = torch.cuda.Event()
@@ -70,6 +74,10 @@ class HostAttentionStep:
 
     def step(self, hQ, hK, hV, hdO, hO, hLSE, hdQ, hdK, hdV) -> None:
         torch = self.torch
+        n = self.B * self.H
+        # [B, H, ...] contiguous == [B*H, 1, ...]
+        hQ, hK, hV, hdO, hO, hdQ, hdK, hdV = (x.view(n, 1, self.T, 64) for x in (hQ, hK, hV, hdO, hO, hdQ, hdK, hdV))
+        hLSE = hLSE.view(n, 1, self.T)
         cur = torch.cuda.current_stream(self.device)
         self.ev_start.record(cur)
         for s in (self.s_in, self.s_cmp, self.s_out):
