@@ -17,8 +17,11 @@
 // compute warps -- are directly the tensor-memory A operands of dV += P^T dO and
 // dK += dS^T Q.  dS is also staged once through shared memory (MN-major) as the
 // A operand of dQ = dS K.  dV, dK (64 columns each) stay in tensor memory for
-// the whole CTA; dQ (64 columns) is drained per query tile with vectorised fp32
-// reductions.
+// the whole CTA; dQ (64 columns) is drained per query tile.  Everything the
+// kernel writes leaves through shared memory and the TMA unit: dQ tiles are
+// added to global memory with bulk reductions (per-thread atomics stall the
+// tensor-core instruction issue of the same SM), dV and dK are stored with bulk
+// copies at the end (a thread-per-row store touches 32 lines per instruction).
 //
 // Q, dO and K each feed one product that contracts over d (K-major operand,
 // 16-byte-chunk swizzle) and one that contracts over the sequence (MN-major
@@ -26,13 +29,15 @@
 // each of them into shared memory twice, once per swizzle.  The MN-major copies
 // of Q and dO are dead once dV and dK have consumed them, and dS is staged over
 // them for dQ = dS K; the K-major copies are free as soon as S^T and dP^T are
-// done, so the next query tile's are prefetched a whole tile ahead.
+// done, so the next query tile's are prefetched a whole tile ahead (dQ of the
+// previous tile passes through the K-major dO buffer first).
 //
 // Tensor-pipe order per query tile i:  dV(i), dK(i) | S^T(i+1), dP^T(i+1) | dQ(i).
-// The compute warps work on tile i+1 while dQ(i) executes, and write dS(i) to
-// shared memory while S^T(i+1), dP^T(i+1) execute.
+// The compute warps start the exponentials of tile i+1 as soon as S^T(i+1) is
+// done, work on it while dP^T(i+1) and dQ(i) execute, and write dS(i) to shared
+// memory while S^T(i+1), dP^T(i+1) execute.
 //
-//   warp 0     TMA producer (K, V once; Q and dO per query tile)
+//   warp 0     TMA producer (K, V once; Q and dO per query tile; dQ, dK, dV out)
 //   warp 1     MMA issuer
 //   warps 2-17 compute: four threads per key row (tensor-memory lane), each
 //              owning 32 of the 128 query columns, all held in registers so
