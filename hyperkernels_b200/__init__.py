@@ -31,4 +31,5 @@ from .attention import (  # noqa: F401
     FLAG_REUSE_FWD_ROUNDED,
     FLAG_DROPOUT_SCALED,
 )
+from .graph_step import GraphedAttentionStep  # noqa: F401
 from .host_step import HostAttentionStep  # noqa: F401

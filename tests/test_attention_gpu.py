@@ -494,6 +494,27 @@ def test_host_step_pipeline_matches_direct_calls(chunks):
     assert hs.h2d_bytes == 4 * Q.nbytes and hs.d2h_bytes == 4 * Q.nbytes + LSE.numel() * 4
 
 
+def test_graphed_step_replays_the_direct_calls():
+    """GraphedAttentionStep (forward + backward captured in a CUDA graph): a replay gives what the direct calls give,
+    also after the inputs were refilled in place."""
+    B, H, T = 2, 3, 320
+    tQ, tK, tV, tdO = (dev(normal((B, H, T, 64), 90 + s)) for s in range(4))
+    gs = hk.GraphedAttentionStep(tQ, tK, tV, tdO, SCALE, True)
+    assert gs.launches_per_replay == 4
+    for seed in (0, 1):
+        if seed:
+            for t_, s in zip((tQ, tK, tV, tdO), range(4)):
+                t_.copy_(dev(normal((B, H, T, 64), 95 + s)))
+        gs.replay()
+        torch.cuda.synchronize()
+        ok_status()
+        O, LSE = hk.attention_forward(tQ, tK, tV, SCALE, 1)
+        dQ, dK, dV, _ = hk.attention_backward(tQ, tK, tV, O, tdO, LSE, SCALE, 1)
+        assert torch.equal(gs.O, O) and torch.equal(gs.LSE, LSE)
+        assert torch.equal(gs.dK, dK) and torch.equal(gs.dV, dV)
+        assert float((gs.dQ - dQ).abs().max()) <= 1e-4
+
+
 def test_merge_partial_equals_full():
     """Keys split into two blocks, each attended separately, merged: equals attention over all keys."""
     B, H, Tq, Tk = 2, 2, 200, 384
