@@ -67,7 +67,7 @@ class MemEfficientFwdParams(C.Structure):
         ("dropout_seed", C.c_uint64), ("dropout_offset", C.c_uint64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("kv_len", C.c_int64), ("q_pos0", C.c_int64), ("k_pos0", C.c_int64),
-        ("flags", C.c_uint32), ("reserved", C.c_uint32),
+        ("flags", C.c_uint32), ("bh_pos0", C.c_uint32),
     ]
 
 
@@ -93,6 +93,7 @@ class MemEfficientBwdParams(C.Structure):
         ("dropout_seed", C.c_uint64), ("dropout_offset", C.c_uint64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("kv_len", C.c_int64), ("q_pos0", C.c_int64), ("k_pos0", C.c_int64),
+        ("bh_pos0", C.c_uint32), ("reserved", C.c_uint32),
     ]
 
 
@@ -125,6 +126,8 @@ def lib() -> C.CDLL:
         L.hk_attn_merge_partial.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         L.hk_attn_dropout_mask.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_float, C.c_uint64,
                                            C.c_uint64, C.c_int64, C.c_int64]
+        L.hk_attn_dropout_mask_slices.argtypes = [C.c_void_p, C.c_uint32, C.c_int, C.c_int64, C.c_int64, C.c_float,
+                                                  C.c_uint64, C.c_uint64, C.c_int64, C.c_int64]
         L.hk_attn_last_device_status.restype = C.c_int
         L.hk_attn_launch_count.restype = C.c_uint64
         L.hk_attn_round_tf32.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
@@ -185,12 +188,15 @@ def launch_count() -> int:
     return int(lib().hk_attn_launch_count())
 
 
-def dropout_keep_mask(BH: int, Tq: int, Tk: int, p: float, seed: int, offset: int, q_pos0: int = 0, k_pos0: int = 0):
-    """Host twin of the in-kernel Philox mask, in the reference's dense format (numpy [BH,Tq,Tk] of 1.0/0.0)."""
+def dropout_keep_mask(BH: int, Tq: int, Tk: int, p: float, seed: int, offset: int, q_pos0: int = 0, k_pos0: int = 0,
+                      bh_pos0: int = 0):
+    """Host twin of the in-kernel Philox mask, in the reference's dense format (numpy [BH,Tq,Tk] of 1.0/0.0);
+    bh_pos0 = index of the first (batch, head) slice when the BH slices are a run out of a larger problem."""
     import numpy as np
 
     m = np.empty((BH, Tq, Tk), dtype=np.float32)
-    _check(lib().hk_attn_dropout_mask(m.ctypes.data, BH, Tq, Tk, p, seed, offset, q_pos0, k_pos0), "hk_attn_dropout_mask")
+    _check(lib().hk_attn_dropout_mask_slices(m.ctypes.data, bh_pos0, BH, Tq, Tk, p, seed, offset, q_pos0, k_pos0),
+           "hk_attn_dropout_mask_slices")
     return m
 
 
@@ -223,8 +229,8 @@ def _workspace(nbytes: int, like, workspace):
 
 def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float = 0.0, dropout_mask=None,
                       philox_seed: Optional[int] = None, philox_offset: int = 0, q_pos0: int = 0, k_pos0: int = 0,
-                      prerounded: bool = False, dropout_scaled: bool = False, workspace=None, out=None, lse=None,
-                      stream=None):
+                      bh_pos0: int = 0, prerounded: bool = False, dropout_scaled: bool = False, workspace=None,
+                      out=None, lse=None, stream=None):
     """O, LSE = fused attention forward of [B,H,Tq,64] Q against [B,H,Tk,64] K, V (fp32 CUDA tensors)."""
     import torch
 
@@ -241,7 +247,7 @@ def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float =
         _set3(p, name, t)
     p.lse_strideB, p.lse_strideH = LSE.stride(0), LSE.stride(1)
     p.kv_len = Tk if Tk != Tq else 0
-    p.q_pos0, p.k_pos0 = q_pos0, k_pos0
+    p.q_pos0, p.k_pos0, p.bh_pos0 = q_pos0, k_pos0, bh_pos0
     flags = 0
     if philox_seed is not None:
         flags |= FLAG_PHILOX_DROPOUT
@@ -260,7 +266,7 @@ def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float =
 
 def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropout_p: float = 0.0, dropout_mask=None,
                        philox_seed: Optional[int] = None, philox_offset: int = 0, q_pos0: int = 0, k_pos0: int = 0,
-                       prerounded: bool = False, D=None, d_precomputed: bool = False, accum_dkdv: bool = False,
+                       bh_pos0: int = 0, prerounded: bool = False, D=None, d_precomputed: bool = False, accum_dkdv: bool = False,
                        accum_dq: bool = False, reuse_fwd_rounded: bool = False, dropout_scaled: bool = False,
                        workspace=None, dQ=None, dK=None, dV=None, stream=None):
     """dQ, dK, dV, D = fused attention backward (fp32 CUDA tensors, [B,H,T,64])."""
@@ -288,7 +294,7 @@ def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropo
     p.dropout_p = dropout_p
     p.dropout_mask = dropout_mask.data_ptr() if dropout_mask is not None else None
     p.kv_len = Tk if Tk != Tq else 0
-    p.q_pos0, p.k_pos0 = q_pos0, k_pos0
+    p.q_pos0, p.k_pos0, p.bh_pos0 = q_pos0, k_pos0, bh_pos0
     flags = 0
     if philox_seed is not None:
         flags |= FLAG_PHILOX_DROPOUT

@@ -42,6 +42,8 @@
 //   warps 2-17 compute: four threads per key row (tensor-memory lane), each
 //              owning 32 of the 128 query columns, all held in registers so
 //              that S^T and dP^T are read from tensor memory exactly once
+#include <mutex>
+
 #include "attn_kernels.cuh"
 #include "philox.h"
 
@@ -84,9 +86,13 @@ static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may opt in to");
 
 // Timeline slots (SM clock): role r in {0: MMA issuer, 1: compute thread 0}, iteration it, phase ph:
 // buffer[1 + (it * 2 + r) * 8 + ph]; buffer[0] = number of iterations of the recorded CTA.
+#ifdef HK_TIMELINE
 __device__ __forceinline__ void stamp(const BwdArgs& a, bool on, int it, int role, int ph) {
     if (on && it < 200) a.timeline[1 + (it * 2 + role) * 8 + ph] = clock64();
 }
+#else
+__device__ __forceinline__ void stamp(const BwdArgs&, bool, int, int, int) {}
+#endif
 
 enum WaitId {
     W_KVFULL = 201, W_QKFULL, W_QKEMPTY, W_QMFULL, W_QMFREE, W_SFULL, W_PREADY, W_BDONE, W_DSREADY, W_DQFULL, W_DQEMPTY,
@@ -105,7 +111,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     using namespace bwd;
     extern __shared__ __align__(1024) uint8_t smem[];
     // schedule trace (timeline_block < 0): {start ns, end ns, SM id, query tiles} of each of the first 1024 CTAs
+#ifdef HK_TIMELINE
     const bool trace = a.timeline != nullptr && a.timeline_block < 0 && blockIdx.x < 1024 && threadIdx.x == 0;
+#else
+    constexpr bool trace = false;
+#endif
     if (trace) {
         a.timeline[4 * blockIdx.x] = (long long)globaltimer_ns();
         a.timeline[4 * blockIdx.x + 2] = smid();
@@ -175,7 +185,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem = sh.tmem_base;
     WaitCtx wc{&sh.abort_flag, a.status};
+#ifdef HK_TIMELINE
     const bool tl = a.timeline != nullptr && (int)blockIdx.x == a.timeline_block;  // never in trace mode
+#else
+    constexpr bool tl = false;
+#endif
     if (tl && threadIdx.x == 0) a.timeline[0] = n_it;
 
     if (warp == 0) {
@@ -442,7 +456,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 uint32_t mine = 0u;  // bit 8m + u: query column c0 + 8m + j8, key row (row & ~7) + u
 #pragma unroll
                 for (int mI = 0; mI < 4; ++mI) {
-                    const hk_philox4_t w = hk_philox_row8(a.seed, a.offset, (uint32_t)bh,
+                    const hk_philox4_t w = hk_philox_row8(a.seed, a.offset, a.bh_pos0 + (uint32_t)bh,
                                                           (uint32_t)(a.q_pos0 + q0 + c0 + 8 * mI + j8), kgrp);
                     mine |= hk_philox_keep8(w, a.drop_thr) << (8 * mI);
                 }
@@ -627,15 +641,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 }
 
 int launch_attn_bwd(const BwdMaps& m, const BwdArgs& a, cudaStream_t stream) {
-    static bool attr_done[64] = {};
+    // the opt-in to large dynamic shared memory is per device: once per device, safe from any number of host threads
+    static std::once_flag attr_once[HK_MAX_DEVICES];
+    static cudaError_t attr_rc[HK_MAX_DEVICES];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return HK_ERR_CUDA;
-    if (dev < 64 && !attr_done[dev]) {
-        if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd::SMEM_BYTES) !=
-            cudaSuccess)
-            return HK_ERR_CUDA;
-        attr_done[dev] = true;
-    }
+    if (dev < 0 || dev >= HK_MAX_DEVICES) return HK_ERR_UNSUPPORTED;
+    std::call_once(attr_once[dev], [dev] {
+        attr_rc[dev] = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bwd::SMEM_BYTES);
+    });
+    if (attr_rc[dev] != cudaSuccess) return HK_ERR_CUDA;
     const long long nblocks = (long long)a.n_kvtiles * a.BH;
     if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
     timing_mark(TIMED_BWD, true, stream);

@@ -12,6 +12,7 @@
 
 namespace hk {
 
+constexpr int HK_MAX_DEVICES = 64;  // device ordinals the per-device caches cover
 constexpr int HEAD_DIM = 64;
 constexpr int TILE = 128;                      // query rows and key rows per MMA tile
 constexpr int HALF_D = 32;                     // floats per 128-byte swizzle row

@@ -27,6 +27,8 @@
 //                 use the same maximum, so the result is the same function).
 // Tensor memory: S_0, S_1 (128 columns each), O_0, O_1 (64 columns each).
 // Warps 0-3 give most of their registers to the softmax warps (setmaxnreg).
+#include <mutex>
+
 #include "attn_kernels.cuh"
 #include "philox.h"
 
@@ -58,9 +60,13 @@ enum WaitId { W_QFULL = 101, W_KFULL, W_KEMPTY, W_VFULL, W_VEMPTY, W_SFULL, W_PF
 
 // Timeline slots (SM clock): role 0 = MMA issuer, 1 = softmax thread 0 of tile 0, 2 = of tile 1;
 // buffer[1 + (j * 3 + role) * 8 + ph]; buffer[0] = number of KV steps of the recorded CTA.
+#ifdef HK_TIMELINE
 __device__ __forceinline__ void stamp(const FwdArgs& a, bool on, int j, int role, int ph) {
     if (on && j < 150) a.timeline[1 + (j * 3 + role) * 8 + ph] = clock64();
 }
+#else
+__device__ __forceinline__ void stamp(const FwdArgs&, bool, int, int, int) {}
+#endif
 
 // 384 threads x 168 registers at launch = 128 x 48 + 256 x 224 after the hand-over
 __device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 48;\n"); }
@@ -86,7 +92,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     using namespace fwd;
     extern __shared__ __align__(1024) uint8_t smem[];
     // schedule trace (timeline_block < 0): {start ns, end ns, SM id, key tiles} of each of the first 1024 CTAs
+#ifdef HK_TIMELINE
     const bool trace = a.timeline != nullptr && a.timeline_block < 0 && blockIdx.x < 1024 && threadIdx.x == 0;
+#else
+    constexpr bool trace = false;
+#endif
     if (trace) {
         a.timeline[4 * blockIdx.x] = (long long)globaltimer_ns();
         a.timeline[4 * blockIdx.x + 2] = smid();
@@ -138,7 +148,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t tmem = sh.tmem_base;
     WaitCtx wc{&sh.abort_flag, a.status};
+#ifdef HK_TIMELINE
     const bool tl = a.timeline != nullptr && (int)blockIdx.x == a.timeline_block;
+#else
+    constexpr bool tl = false;
+#endif
     if (tl && threadIdx.x == 0) a.timeline[0] = n;
 
     if (warp < 4) {
@@ -353,7 +367,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #pragma unroll
                 for (int g = 0; g < 16; ++g) {
                     const uint32_t kpos = (uint32_t)(a.k_pos0 + kv0 + g * 8);
-                    const hk_philox4_t w = hk_philox_row8(a.seed, a.offset, (uint32_t)bh, (uint32_t)(a.q_pos0 + qrow), kpos >> 3);
+                    const hk_philox4_t w = hk_philox_row8(a.seed, a.offset, a.bh_pos0 + (uint32_t)bh, (uint32_t)(a.q_pos0 + qrow), kpos >> 3);
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
                         float p = ex2_approx(fmaf(__uint_as_float(r[g * 8 + u]), c, neg_m));
@@ -442,15 +456,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 
 int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                     const FwdArgs& a, cudaStream_t stream) {
-    static bool attr_done[64] = {};
+    // the opt-in to large dynamic shared memory is per device: once per device, safe from any number of host threads
+    static std::once_flag attr_once[HK_MAX_DEVICES];
+    static cudaError_t attr_rc[HK_MAX_DEVICES];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return HK_ERR_CUDA;
-    if (dev < 64 && !attr_done[dev]) {
-        if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd::SMEM_BYTES) !=
-            cudaSuccess)
-            return HK_ERR_CUDA;
-        attr_done[dev] = true;
-    }
+    if (dev < 0 || dev >= HK_MAX_DEVICES) return HK_ERR_UNSUPPORTED;
+    std::call_once(attr_once[dev], [dev] {
+        attr_rc[dev] = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd::SMEM_BYTES);
+    });
+    if (attr_rc[dev] != cudaSuccess) return HK_ERR_CUDA;
     const long long nblocks = (long long)a.n_qtiles * a.BH;
     if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
     timing_mark(TIMED_FWD, true, stream);

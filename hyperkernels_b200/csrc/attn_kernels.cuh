@@ -19,9 +19,10 @@ struct FwdArgs {
     int drop_scaled;   // 1: inverted dropout (normaliser over all visible keys, kept terms times keep_scale)
     float keep_scale;  // 1/(1-p) when drop_scaled, else 1
     uint32_t drop_thr;
+    uint32_t bh_pos0;  // added to the local (batch, head) index in the Philox counter
     uint64_t seed, offset;
     DeviceStatus* status;
-    long long* timeline;  // optional: per-phase SM clock stamps of one CTA (hk_attn_debug_timeline)
+    long long* timeline;  // per-phase SM clock stamps of one CTA; only builds with -DHK_TIMELINE read it
     int timeline_block;
 };
 
@@ -50,9 +51,10 @@ struct BwdArgs {
     float dp_scale;    // factor of dP inside dS: scale, times 1/(1-p) when drop_scaled
     float dv_scale;    // factor of the dV accumulator: 1/(1-p) when drop_scaled, else 1
     uint32_t drop_thr;
+    uint32_t bh_pos0;  // added to the local (batch, head) index in the Philox counter
     uint64_t seed, offset;
     DeviceStatus* status;
-    long long* timeline;  // optional: per-phase SM clock stamps of one CTA (hk_attn_debug_timeline)
+    long long* timeline;  // per-phase SM clock stamps of one CTA; only builds with -DHK_TIMELINE read it
     int timeline_block;
 };
 
@@ -67,6 +69,5 @@ struct BwdMaps {
 int launch_attn_bwd(const BwdMaps& m, const BwdArgs& a, cudaStream_t stream);
 
 int run_umma_selftest(int which, const float* A, const float* B, float* out, cudaStream_t stream);
-int run_umma_peak(int mode, int iters, int ctas, const float* A, const float* B, double* flops_out, cudaStream_t stream);
 
 }  // namespace hk

@@ -30,8 +30,9 @@ __global__ void __launch_bounds__(256) round_tf32_kernel(const RoundJob job) {
         const int bh = (int)(row / T);
         const int r = (int)(row - (long long)bh * T);
         const int b = bh / H, h = bh - b * H;
+        // plain load: dst may be src (hk_attn_round_tf32 in place), which rules the read-only path out
         const float4 x =
-            __ldg(reinterpret_cast<const float4*>(v.ptr + (int64_t)b * v.sB + (int64_t)h * v.sH + (int64_t)r * v.sM) + c4);
+            *(reinterpret_cast<const float4*>(v.ptr + (int64_t)b * v.sB + (int64_t)h * v.sH + (int64_t)r * v.sM) + c4);
         uint4 y;
         y.x = tf32_round_bits(__float_as_uint(x.x));
         y.y = tf32_round_bits(__float_as_uint(x.y));
@@ -108,13 +109,17 @@ int launch_precompute_D(const DJob& j, cudaStream_t stream) {
 
 // ---------------------------------------------------------------------------
 // The same row sum for the other head dimensions the reference instantiates
-// (mem_efficient_bwd_precompute_D_sm89.cu:93-102: 16 ... 256): HD/4 lanes per
-// row (at most a warp; two float4 per lane for 256), shuffle reduction.
+// (mem_efficient_bwd_precompute_D_sm89.cu:93-102: 16, 32, 48, 64, 80, 96, 128,
+// 160, 192, 256).  A row of HD floats is HD/4 float4; LANES lanes (a power of
+// two, at most a warp) share a row and each takes every LANES-th float4, so
+// the dimensions that are not powers of two leave some lanes idle in the last
+// round; shuffle reduction within the group.
 // ---------------------------------------------------------------------------
 template <int HD>
 __global__ void __launch_bounds__(256) precompute_D_hd_kernel(const DJob j) {
-    constexpr int LANES = (HD / 4 < 32) ? HD / 4 : 32;  // lanes that share a row
-    constexpr int VEC = HD / 4 / LANES;                  // float4 per lane
+    constexpr int NV = HD / 4;                                        // float4 per row
+    constexpr int LANES = NV >= 32 ? 32 : NV >= 16 ? 16 : NV >= 8 ? 8 : 4;  // lanes that share a row
+    constexpr int ROUNDS = (NV + LANES - 1) / LANES;
     const long long nrows = (long long)j.BH * j.T;
     const int sub = threadIdx.x % LANES;
     const long long stride = ((long long)gridDim.x * blockDim.x) / LANES;
@@ -132,9 +137,12 @@ __global__ void __launch_bounds__(256) precompute_D_hd_kernel(const DJob j) {
             const float4* o4 = reinterpret_cast<const float4*>(j.O.ptr + (int64_t)b * j.O.sB + (int64_t)h * j.O.sH +
                                                                (int64_t)r * j.O.sM);
 #pragma unroll
-            for (int v = 0; v < VEC; ++v) {
-                const float4 g = __ldg(g4 + sub + v * LANES), o = __ldg(o4 + sub + v * LANES);
-                s += g.x * o.x + g.y * o.y + g.z * o.z + g.w * o.w;
+            for (int v = 0; v < ROUNDS; ++v) {
+                const int c = sub + v * LANES;
+                if (NV % LANES == 0 || c < NV) {
+                    const float4 g = __ldg(g4 + c), o = __ldg(o4 + c);
+                    s += g.x * o.x + g.y * o.y + g.z * o.z + g.w * o.w;
+                }
             }
         }
 #pragma unroll
@@ -143,17 +151,29 @@ __global__ void __launch_bounds__(256) precompute_D_hd_kernel(const DJob j) {
     }
 }
 
+template <int HD>
+static void launch_D_hd(const DJob& j, cudaStream_t stream) {
+    constexpr int NV = HD / 4;
+    constexpr int LANES = NV >= 32 ? 32 : NV >= 16 ? 16 : NV >= 8 ? 8 : 4;
+    const long long nrows = (long long)j.BH * j.T;
+    const int blocks = (int)std::min<long long>((nrows * LANES + 255) / 256, 148 * 8);
+    precompute_D_hd_kernel<HD><<<blocks, 256, 0, stream>>>(j);
+}
+
 int launch_precompute_D_hd(const DJob& j, int head_dim, cudaStream_t stream) {
     const long long nrows = (long long)j.BH * j.T;
     if (nrows == 0) return HK_OK;
-    const int lanes = head_dim / 4 < 32 ? head_dim / 4 : 32;
-    const int blocks = (int)std::min<long long>((nrows * lanes + 255) / 256, 148 * 8);
     switch (head_dim) {
-        case 16: precompute_D_hd_kernel<16><<<blocks, 256, 0, stream>>>(j); break;
-        case 32: precompute_D_hd_kernel<32><<<blocks, 256, 0, stream>>>(j); break;
-        case 64: precompute_D_hd_kernel<64><<<blocks, 256, 0, stream>>>(j); break;
-        case 128: precompute_D_hd_kernel<128><<<blocks, 256, 0, stream>>>(j); break;
-        case 256: precompute_D_hd_kernel<256><<<blocks, 256, 0, stream>>>(j); break;
+        case 16: launch_D_hd<16>(j, stream); break;
+        case 32: launch_D_hd<32>(j, stream); break;
+        case 48: launch_D_hd<48>(j, stream); break;
+        case 64: launch_D_hd<64>(j, stream); break;
+        case 80: launch_D_hd<80>(j, stream); break;
+        case 96: launch_D_hd<96>(j, stream); break;
+        case 128: launch_D_hd<128>(j, stream); break;
+        case 160: launch_D_hd<160>(j, stream); break;
+        case 192: launch_D_hd<192>(j, stream); break;
+        case 256: launch_D_hd<256>(j, stream); break;
         default: return HK_ERR_UNSUPPORTED;
     }
     count_launch();

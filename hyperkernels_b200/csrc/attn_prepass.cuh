@@ -23,7 +23,7 @@ struct DJob {
     int H, BH, T;
 };
 int launch_precompute_D(const DJob& j, cudaStream_t stream);
-// D only, head dimension 16, 32, 64, 128 or 256 (dO_rounded and dQ_zero are ignored)
+// D only, head dimension 16, 32, 48, 64, 80, 96, 128, 160, 192 or 256 (dO_rounded and dQ_zero are ignored)
 int launch_precompute_D_hd(const DJob& j, int head_dim, cudaStream_t stream);
 
 int launch_zero_rows(float* ptr, int64_t sB, int64_t sM, int64_t sH, int B, int H, int T, cudaStream_t stream);

@@ -26,7 +26,7 @@ static_assert(offsetof(hk_attn_bwd_params, D) == 48 && offsetof(hk_attn_bwd_para
 static_assert(offsetof(hk_attn_bwd_params, B) == 80 && offsetof(hk_attn_bwd_params, T) == 88, "bwd head");
 static_assert(offsetof(hk_attn_bwd_params, scale) == 92 && offsetof(hk_attn_bwd_params, is_causal) == 96, "bwd head");
 static_assert(offsetof(hk_attn_bwd_params, q_strideB) == 104 && offsetof(hk_attn_bwd_params, d_strideH) == 320, "bwd head");
-static_assert(sizeof(hk_attn_fwd_params) == 256 && sizeof(hk_attn_bwd_params) == 400, "block sizes");
+static_assert(sizeof(hk_attn_fwd_params) == 256 && sizeof(hk_attn_bwd_params) == 408, "block sizes");
 static_assert(offsetof(hk_attn_bwd_params, dropout_p) == 328, "bwd tail starts after the 328-byte reference block");
 
 namespace hk {
@@ -65,10 +65,10 @@ int check_launch() {
 __device__ DeviceStatus g_device_status;  // one instance per device that loads the module
 
 DeviceStatus* device_status_ptr() {
-    static DeviceStatus* cache[64] = {};
+    static DeviceStatus* cache[HK_MAX_DEVICES] = {};
     static std::mutex mu;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= HK_MAX_DEVICES) return nullptr;
     std::lock_guard<std::mutex> lock(mu);
     if (!cache[dev]) {
         void* p = nullptr;
@@ -111,12 +111,14 @@ int make_tile_map(CUtensorMap* map, const float* ptr, int inner, int B, int H, i
 }
 
 // ---- optional phase timeline of one CTA (performance debugging) ------------------
-static long long* g_timeline = nullptr;
-static int g_timeline_block = 0;
+static std::atomic<long long*> g_timeline{nullptr};
+static std::atomic<int> g_timeline_block{0};
 
 // ---- validation helpers -------------------------------------------------------
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline bool stride_ok(int64_t s) { return s >= 0 && (s % 4) == 0; }
+// A stride of 0 would broadcast one slice over batches or heads; the TMA tensor maps cannot express that.
+static inline bool broadcast_stride(int n, int64_t s) { return n > 1 && s == 0; }
 static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 }  // namespace hk
@@ -182,6 +184,11 @@ int hk_attn_last_device_status(void) {
 
 int hk_attn_dropout_mask(float* mask, int BH, int64_t Tq, int64_t Tk, float p, uint64_t seed, uint64_t offset,
                          int64_t q_pos0, int64_t k_pos0) {
+    return hk_attn_dropout_mask_slices(mask, 0u, BH, Tq, Tk, p, seed, offset, q_pos0, k_pos0);
+}
+
+int hk_attn_dropout_mask_slices(float* mask, uint32_t bh_pos0, int BH, int64_t Tq, int64_t Tk, float p, uint64_t seed,
+                                uint64_t offset, int64_t q_pos0, int64_t k_pos0) {
     if (!mask) return HK_ERR_NULL_POINTER;
     if (!(p >= 0.f && p < 1.f)) return HK_ERR_BAD_DROPOUT;
     if (BH < 0 || Tq < 0 || Tk < 0) return HK_ERR_BAD_SHAPE;
@@ -190,7 +197,7 @@ int hk_attn_dropout_mask(float* mask, int BH, int64_t Tq, int64_t Tk, float p, u
         for (int64_t i = 0; i < Tq; ++i) {
             float* row = mask + ((size_t)bh * Tq + i) * Tk;
             for (int64_t j = 0; j < Tk; ++j)
-                row[j] = hk_philox_keep(seed, offset, (uint32_t)bh, (uint32_t)(q_pos0 + i), (uint32_t)(k_pos0 + j), thr)
+                row[j] = hk_philox_keep(seed, offset, bh_pos0 + (uint32_t)bh, (uint32_t)(q_pos0 + i), (uint32_t)(k_pos0 + j), thr)
                              ? 1.0f
                              : 0.0f;
         }
@@ -253,6 +260,12 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
         if (!stride_ok(s)) return HK_ERR_MISALIGNED;
     if (p->q_strideM < HEAD_DIM || p->k_strideM < HEAD_DIM || p->v_strideM < HEAD_DIM || p->o_strideM < HEAD_DIM)
         return HK_ERR_BAD_SHAPE;
+    {
+        const int64_t sb[] = {p->q_strideB, p->k_strideB, p->v_strideB, p->o_strideB};
+        const int64_t sh[] = {p->q_strideH, p->k_strideH, p->v_strideH, p->o_strideH};
+        for (int i = 0; i < 4; ++i)
+            if (broadcast_stride(p->B, sb[i]) || broadcast_stride(p->nh, sh[i])) return HK_ERR_UNSUPPORTED;
+    }
     if (!std::isfinite(p->scale) || p->scale == 0.f) return HK_ERR_BAD_SHAPE;  // masking multiplies -inf by the scale
     int mode = 0;
     int rc = validate_dropout(p->dropout_p, p->dropout_mask, p->flags, p->k_pos0, &mode);
@@ -299,11 +312,11 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     a.keep_scale = keep_scale_of(p->dropout_p, mode, p->flags);
     a.drop_scaled = (mode != 0 && (p->flags & HK_FLAG_DROPOUT_SCALED)) ? 1 : 0;
     a.drop_thr = hk_philox_threshold(p->dropout_p);
-    a.seed = p->dropout_seed; a.offset = p->dropout_offset;
+    a.seed = p->dropout_seed; a.offset = p->dropout_offset; a.bh_pos0 = p->bh_pos0;
     a.status = device_status_ptr();
     if (!a.status) return HK_ERR_CUDA;
-    a.timeline = g_timeline;
-    a.timeline_block = g_timeline_block;
+    a.timeline = g_timeline.load();
+    a.timeline_block = g_timeline_block.load();
     CUtensorMap mo;
     if ((rc = make_tile_map(&mo, p->O, HEAD_DIM, B, H, Tq, p->o_strideB, p->o_strideM, p->o_strideH, TILE))) return rc;
     return launch_attn_fwd(mq, mk, mv, mo, a, stream);
@@ -318,6 +331,7 @@ int hk_attn_bwd_precompute_D(const hk_attn_bwd_params* p, void* stream_) {
     const int64_t st[] = {p->o_strideB, p->o_strideM, p->o_strideH, p->do_strideB, p->do_strideM, p->do_strideH};
     for (int64_t s : st)
         if (!stride_ok(s)) return HK_ERR_MISALIGNED;
+    if (p->o_strideM < HEAD_DIM || p->do_strideM < HEAD_DIM) return HK_ERR_BAD_SHAPE;
     DJob j{};
     j.dO = View4{p->dO, p->do_strideB, p->do_strideM, p->do_strideH};
     j.O = View4{p->O, p->o_strideB, p->o_strideM, p->o_strideH};
@@ -333,7 +347,13 @@ int hk_attn_bwd_precompute_D_hd(const hk_attn_bwd_params* p, int head_dim, void*
     if (!p) return HK_ERR_NULL_POINTER;
     if (!p->dO || !p->O || !p->D) return HK_ERR_NULL_POINTER;
     if (p->B <= 0 || p->nh <= 0 || p->T <= 0) return HK_ERR_BAD_SHAPE;
-    if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256) return HK_ERR_UNSUPPORTED;
+    {
+        // the ten instantiations of mem_efficient_bwd_precompute_D_sm89.cu:93-102
+        static const int dims[] = {16, 32, 48, 64, 80, 96, 128, 160, 192, 256};
+        bool known = false;
+        for (int d : dims) known = known || d == head_dim;
+        if (!known) return HK_ERR_UNSUPPORTED;
+    }
     if (!aligned16(p->dO) || !aligned16(p->O)) return HK_ERR_MISALIGNED;
     const int64_t st[] = {p->o_strideB, p->o_strideM, p->o_strideH, p->do_strideB, p->do_strideM, p->do_strideH};
     for (int64_t s : st)
@@ -371,7 +391,13 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     if (p->q_strideM < HEAD_DIM || p->k_strideM < HEAD_DIM || p->v_strideM < HEAD_DIM || p->do_strideM < HEAD_DIM ||
         p->dq_strideM < HEAD_DIM || p->dk_strideM < HEAD_DIM || p->dv_strideM < HEAD_DIM)
         return HK_ERR_BAD_SHAPE;
-    if (!std::isfinite(p->scale)) return HK_ERR_BAD_SHAPE;
+    {
+        const int64_t sb[] = {p->q_strideB, p->k_strideB, p->v_strideB, p->do_strideB, p->dq_strideB, p->dk_strideB, p->dv_strideB};
+        const int64_t sh[] = {p->q_strideH, p->k_strideH, p->v_strideH, p->do_strideH, p->dq_strideH, p->dk_strideH, p->dv_strideH};
+        for (int i = 0; i < 7; ++i)
+            if (broadcast_stride(p->B, sb[i]) || broadcast_stride(p->nh, sh[i])) return HK_ERR_UNSUPPORTED;
+    }
+    if (!std::isfinite(p->scale) || p->scale == 0.f) return HK_ERR_BAD_SHAPE;  // as in the forward
     int mode = 0;
     int rc = validate_dropout(p->dropout_p, p->dropout_mask, p->flags, p->k_pos0, &mode);
     if (rc != HK_OK) return rc;
@@ -461,11 +487,11 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     a.dv_scale = keep_scale_of(p->dropout_p, mode, p->flags);
     a.dp_scale = p->scale * a.dv_scale;
     a.drop_thr = hk_philox_threshold(p->dropout_p);
-    a.seed = p->dropout_seed; a.offset = p->dropout_offset;
+    a.seed = p->dropout_seed; a.offset = p->dropout_offset; a.bh_pos0 = p->bh_pos0;
     a.status = device_status_ptr();
     if (!a.status) return HK_ERR_CUDA;
-    a.timeline = g_timeline;
-    a.timeline_block = g_timeline_block;
+    a.timeline = g_timeline.load();
+    a.timeline_block = g_timeline_block.load();
     return launch_attn_bwd(m, a, stream);
 }
 
@@ -493,13 +519,14 @@ int hk_attn_round_tf32(const float* src, float* dst, int64_t rows, void* stream_
     return launch_round_tf32(job, static_cast<cudaStream_t>(stream_));
 }
 
+#ifdef HK_TIMELINE
+// Development builds only: CTA `block` of every forward/backward launch writes SM-clock stamps of its pipeline
+// phases into device_buffer (4096 int64; slot layout in attn_*_sm100.cu); block = -1: every CTA b < 1024 writes
+// {start ns, end ns, SM id, tiles} to slots 4b..4b+3.  nullptr turns it off.
 void hk_attn_debug_timeline(long long* device_buffer, int block) {
-    g_timeline = device_buffer;
-    g_timeline_block = block;
+    g_timeline_block.store(block);
+    g_timeline.store(device_buffer);
 }
-
-int hk_attn_mma_peak(int mode, int iters, int ctas, const float* A, const float* B, double* flops_out, void* stream_) {
-    return run_umma_peak(mode, iters, ctas, A, B, flops_out, static_cast<cudaStream_t>(stream_));
-}
+#endif
 
 }  // extern "C"

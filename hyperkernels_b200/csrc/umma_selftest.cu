@@ -124,109 +124,6 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_cons
     }
 }
 
-// ---------------------------------------------------------------------------
-// Tensor-pipe throughput probe: every CTA loads one operand tile pair, then one
-// thread issues `iters` groups of TF32 MMAs back to back with nothing else in
-// the way.  It gives the rate the attention kernels' MMA shapes can reach, the
-// practical ceiling the roofline of those kernels is read against.
-//   mode 0  S-shape:   8 x (M128 N128 K8), A and B K-major from shared memory
-//   mode 1  PV-shape: 16 x (M128 N64 K8),  A from tensor memory, B MN-major
-//   mode 2  dQ-shape: 16 x (M128 N64 K8),  A and B MN-major from shared memory
-//   mode 3  mode 0 alternating between two accumulators (dependency-chain check)
-//   mode 4  M128 N256 K8, A and B K-major (B rows reused twice), one accumulator
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128, 1)
-umma_peak_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 const __grid_constant__ CUtensorMap mapBm, int mode, int iters, DeviceStatus* status) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* sA = smem;                  // 4 boxes
-    uint8_t* sB = smem + 4 * BOX_BYTES;  // 2 boxes
-    st::Shared& sh = *reinterpret_cast<st::Shared*>(smem + 4 * BOX_BYTES + TILE_BYTES);
-    const int warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) {
-        mbar_init(&sh.full, 1);
-        mbar_init(&sh.done, 1);
-        sh.abort_flag = 0;
-        fence_mbar_init();
-    }
-    if (warp == 0) {
-        tmem_alloc(&sh.tmem_base, 512);
-        tmem_relinquish();
-        tc_fence_before_sync();
-    }
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = sh.tmem_base;
-    WaitCtx wc{&sh.abort_flag, status};
-    if (threadIdx.x == 0) {
-        const bool mn = (mode == 1 || mode == 2);
-        mbar_arrive_expect_tx(&sh.full, 6 * BOX_BYTES);
-        for (int i = 0; i < 4; ++i) tma_load_4d(sA + i * BOX_BYTES, mn ? &mapBm : &mapA, &sh.full, (i & 1) * HALF_D, 0, 0, 0);
-        for (int i = 0; i < 2; ++i) tma_load_4d(sB + i * BOX_BYTES, mn ? &mapBm : &mapB, &sh.full, i * HALF_D, 0, 0, 0);
-        if (mbar_wait(wc, &sh.full, 0, 911)) {
-            tc_fence_after_sync();
-            const uint32_t a_addr = smem_u32(sA), b_addr = smem_u32(sB);
-            for (int it = 0; it < iters; ++it) {
-                if (mode == 0 || mode == 3) {
-                    const uint32_t idesc = make_idesc_tf32(128, 128, false, false);
-                    const uint32_t d = tmem + ((mode == 3 && (it & 1)) ? 128 : 0);
-#pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)
-                        umma_ss_tf32(d, kmajor_desc(a_addr, kk, BOX_BYTES), kmajor_desc(b_addr, kk, BOX_BYTES), idesc, 1);
-                } else if (mode == 1) {
-                    const uint32_t idesc = make_idesc_tf32(128, 64, false, true);
-#pragma unroll
-                    for (int kk = 0; kk < 16; ++kk)
-                        umma_ts_tf32(tmem, tmem + 128 + kk * 8, mnmajor_desc(b_addr, kk, BOX_BYTES), idesc, 1);
-                } else if (mode == 2) {
-                    const uint32_t idesc = make_idesc_tf32(128, 64, true, true);
-#pragma unroll
-                    for (int kk = 0; kk < 16; ++kk)
-                        umma_ss_tf32(tmem, mnmajor_desc(a_addr, kk, BOX_BYTES), mnmajor_desc(b_addr, kk, BOX_BYTES), idesc, 1);
-                } else {
-                    // N = 256: B is 256 rows = the A boxes (rows 0..127) followed by ... the same 8-row groups
-                    // repeated; the data is irrelevant here, the descriptor walks 32 groups of 1024 bytes from sA.
-                    const uint32_t idesc = make_idesc_tf32(128, 256, false, false);
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        umma_ss_tf32(tmem, kmajor_desc(b_addr, kk, BOX_BYTES), kmajor_desc(a_addr, kk, 2 * BOX_BYTES), idesc, 1);
-                }
-            }
-            umma_commit(&sh.done);
-        }
-    }
-    __syncwarp();
-    mbar_wait(wc, &sh.done, 0, 912);
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 0) {
-        __syncwarp();
-        tc_fence_after_sync();
-        tmem_dealloc(tmem, 512);
-    }
-}
-
-// flops_out receives the number of floating-point operations one launch performs.
-int run_umma_peak(int mode, int iters, int ctas, const float* A, const float* B, double* flops_out, cudaStream_t stream) {
-    if (mode < 0 || mode > 4 || iters <= 0 || ctas <= 0) return HK_ERR_UNSUPPORTED;
-    if (!A || !B) return HK_ERR_NULL_POINTER;
-    CUtensorMap ma, mb, mbm;
-    int rc;
-    if ((rc = make_tile_map(&ma, A, 64, 1, 1, 128, 128LL * 64, 64, 128LL * 64, TILE, false)) != HK_OK) return rc;
-    if ((rc = make_tile_map(&mb, B, 64, 1, 1, 128, 128LL * 64, 64, 128LL * 64, TILE, false)) != HK_OK) return rc;
-    if ((rc = make_tile_map(&mbm, B, 64, 1, 1, 128, 128LL * 64, 64, 128LL * 64, TILE, true)) != HK_OK) return rc;
-    if (cudaFuncSetAttribute(umma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, st::SMEM_BYTES) != cudaSuccess)
-        return HK_ERR_CUDA;
-    DeviceStatus* status = device_status_ptr();
-    if (!status) return HK_ERR_CUDA;
-    umma_peak_kernel<<<ctas, 128, st::SMEM_BYTES, stream>>>(ma, mb, mbm, mode, iters, status);
-    count_launch();
-    const double per_group = (mode == 4) ? 4.0 * 2 * 128 * 256 * 8 : 2.0 * 128 * 128 * 64;
-    if (flops_out) *flops_out = per_group * iters * ctas;
-    return check_launch();
-}
-
 int run_umma_selftest(int which, const float* A, const float* B, float* out, cudaStream_t stream) {
     if (which < 0 || which > 3) return HK_ERR_UNSUPPORTED;
     if (!A || !B || !out) return HK_ERR_NULL_POINTER;

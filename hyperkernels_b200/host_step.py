@@ -31,8 +31,8 @@ class HostAttentionStep:
     [B, H, T, 64] (LSE: [B, H, T]).  The call enqueues everything and returns; the caller's current stream waits for
     the last result copy, so a ``torch.cuda.synchronize()`` (or an event on that stream) marks completion.
 
-    With Philox dropout every chunk draws its own mask (offset + chunk index): the keep-mask of a chunked step is not
-    the one a single call over the whole batch would draw.
+    With Philox dropout every chunk passes the index of its first (batch, head) slice (``bh_pos0``) with the same
+    seed and offset, so the keep-mask of a chunked step is the one a single call over the whole batch draws.
     """
 
     def __init__(self, B: int, H: int, T: int, scale: float, causal: bool, *, chunks: Optional[int] = None,
@@ -98,7 +98,7 @@ class HostAttentionStep:
                 self.s_cmp.wait_event(self.ev_in[i])
                 if i >= n_slots:  # the results of the chunk that used this slot have left
                     self.s_cmp.wait_event(self.ev_out[i - n_slots])
-                drop = dict(self.drop, philox_offset=self.philox_offset + i) if self.drop else {}
+                drop = dict(self.drop, philox_offset=self.philox_offset, bh_pos0=i * self.cb) if self.drop else {}
                 att.attention_forward(d["Q"], d["K"], d["V"], self.scale, self.causal, workspace=d["ws"], out=d["O"],
                                       lse=d["LSE"], stream=self.s_cmp, **drop)
                 att.attention_backward(d["Q"], d["K"], d["V"], d["O"], d["dO"], d["LSE"], self.scale, self.causal,

@@ -17,7 +17,14 @@
  *   - All pointers are device pointers owned by the caller; the library never
  *     allocates device memory.  Scratch comes from `workspace`.
  *   - Strides are in elements; the last-dimension stride is 1.  Every pointer
- *     and every stride*4 must be a multiple of 16 bytes.
+ *     and every stride*4 must be a multiple of 16 bytes.  A batch or head
+ *     stride of 0 (one slice broadcast over several batches or heads, which
+ *     the reference's pointer arithmetic allows) is refused with
+ *     HK_ERR_UNSUPPORTED when that dimension is larger than 1: the TMA tensor
+ *     maps the kernels read through cannot express it.
+ *   - Re-entrant: no call keeps state between calls except per-device caches
+ *     that are filled once under a lock, so any number of host threads may
+ *     drive any number of devices and streams.  Device ordinals 0..63.
  *   - Every function returns HK_OK (0) or a negative hk_status; nothing exits
  *     the process or throws.  Kernel launches are asynchronous on `stream`;
  *     device-side faults surface on the caller's next synchronisation, and the
@@ -108,7 +115,9 @@ typedef struct hk_attn_fwd_params {
     int64_t q_pos0; /* global position of query row 0 (causal mask, dropout counter) */
     int64_t k_pos0; /* global position of key row 0 */
     uint32_t flags;
-    uint32_t reserved;
+    uint32_t bh_pos0; /* global index of (batch 0, head 0) of this call in the Philox counter: a caller that
+                       * cuts one problem into several calls over runs of (batch, head) slices passes the
+                       * first slice's index, so every cut draws the mask of the single call; 0 otherwise */
 } hk_attn_fwd_params;
 
 /* ---- backward -----------------------------------------------------------
@@ -152,6 +161,8 @@ typedef struct hk_attn_bwd_params {
     int64_t kv_len;
     int64_t q_pos0;
     int64_t k_pos0;
+    uint32_t bh_pos0; /* as in hk_attn_fwd_params */
+    uint32_t reserved;
 } hk_attn_bwd_params;
 
 /* Replaces the launch of fused_attn_forward_kernel_tc_sm89<64,64,64,1>
@@ -181,7 +192,7 @@ int hk_attn_forward_static_scratch(const hk_attn_fwd_params* p, void* stream);
 int hk_attn_bwd_precompute_D(const hk_attn_bwd_params* p, void* stream);
 
 /* The same pre-pass for the other head dimensions the reference instantiates it for
- * (mem_efficient_bwd_precompute_D_sm89<16|32|64|128|256>,
+ * (mem_efficient_bwd_precompute_D_sm89<16|32|48|64|80|96|128|160|192|256>,
  * kernels/attention/mem_efficient_bwd_precompute_D_sm89.cu:93-102): dO and O rows hold
  * `head_dim` floats.  The attention kernels themselves are head_dim 64 only. */
 int hk_attn_bwd_precompute_D_hd(const hk_attn_bwd_params* p, int head_dim, void* stream);
@@ -207,7 +218,7 @@ int hk_attn_merge_partial(float* O_acc, float* LSE_acc, const float* O_part, con
                           void* stream);
 
 /* Rounds `rows` contiguous rows of 64 floats to TF32 (round to nearest, the reference's
- * `+0x1000`, fused_attn_forward_kernel_tc_sm89.cu:197) from src into dst (may alias).  A caller
+ * `+0x1000`, fused_attn_forward_kernel_tc_sm89.cu:197) from src into dst (dst may be src: in place).  A caller
  * that feeds the same tensor to several calls (the ring schedule does) rounds it once and passes
  * HK_FLAG_OPERANDS_PREROUNDED.  No counterpart in the reference, which rounds at every load. */
 int hk_attn_round_tf32(const float* src, float* dst, int64_t rows, void* stream);
@@ -217,6 +228,10 @@ int hk_attn_round_tf32(const float* src, float* dst, int64_t rows, void* stream)
  * mask[(bh*Tq + i)*Tk + j] = 1.0f keep / 0.0f drop.  `mask` is HOST memory. */
 int hk_attn_dropout_mask(float* mask, int BH, int64_t Tq, int64_t Tk, float p, uint64_t seed, uint64_t offset,
                          int64_t q_pos0, int64_t k_pos0);
+/* The same for (batch, head) slices bh_pos0 .. bh_pos0 + BH - 1 of a larger problem (the mask a call with that
+ * bh_pos0 in its argument block draws). */
+int hk_attn_dropout_mask_slices(float* mask, uint32_t bh_pos0, int BH, int64_t Tq, int64_t Tk, float p, uint64_t seed,
+                                uint64_t offset, int64_t q_pos0, int64_t k_pos0);
 
 /* Reads (and clears) the status word the kernels of this process wrote on the
  * current device: HK_OK, or HK_ERR_DEVICE_TIMEOUT if a bounded wait gave up.
@@ -242,22 +257,6 @@ int hk_attn_kernel_timing_read(int kind, double* total_ms, int* launches);
  * hk_attn_last_device_status() reports HK_ERR_DEVICE_TIMEOUT once; see
  * hyperkernels_b200/csrc/umma_selftest.cu. */
 int hk_attn_selftest(int which, const float* A, const float* B, float* out, void* stream);
-
-/* Performance debugging: while `device_buffer` (device memory, 4096 int64) is set, CTA
- * number `block` of every forward/backward launch writes SM-clock stamps of its
- * pipeline phases into it (slot layout in csrc/attn_*_sm100.cu).  With block = -1 every
- * CTA b < 1024 of a forward or backward launch instead writes {start ns, end ns, SM id, tiles}
- * to slots 4b..4b+3 (the schedule of the launch).  NULL turns it off.
- * No counterpart in the reference. */
-void hk_attn_debug_timeline(long long* device_buffer, int block);
-
-/* Tensor-pipe throughput probe: `ctas` CTAs each issue `iters` groups of the TF32
- * MMA shapes the attention kernels use (mode 0: S = Q K^T shape, 1: O = P V shape,
- * 2: dQ = dS K shape, 3: mode 0 on two alternating accumulators, 4: M128 N256),
- * back to back.  A and B are device [128,64] fp32 matrices.  *flops_out receives
- * the operation count of the launch; time it with events on `stream`.  No
- * counterpart in the reference. */
-int hk_attn_mma_peak(int mode, int iters, int ctas, const float* A, const float* B, double* flops_out, void* stream);
 
 const char* hk_status_string(int status);
 

@@ -40,7 +40,9 @@ def test_reference_block_layouts():
                dropout_p=328)
     for k, v in exp.items():
         assert getattr(BP, k).offset == v, k
-    assert C.sizeof(BP) == 400
+    assert C.sizeof(BP) == 408
+    # extension tails: the Philox (batch, head) base index
+    assert FP.bh_pos0.offset == 252 and BP.bh_pos0.offset == 400
 
 
 def _fwd_block():
@@ -75,12 +77,47 @@ def test_forward_argument_validation():
     assert L.hk_attn_forward(C.byref(p), None) == -6          # unsupported Philox alignment
 
 
+def _bwd_block():
+    p = BP()
+    p.Q = p.K = p.V = p.O = p.dO = p.LSE = p.D = p.dQ = p.dK = p.dV = 0x1000
+    p.B, p.nh, p.T, p.scale = 1, 1, 128, 0.125
+    for n in ("q", "k", "v", "o", "do", "dq", "dk", "dv"):
+        setattr(p, f"{n}_strideB", 128 * 64); setattr(p, f"{n}_strideH", 128 * 64); setattr(p, f"{n}_strideM", 64)
+    p.lse_strideB = p.lse_strideH = p.d_strideB = p.d_strideH = 128
+    p.flags = hk.FLAG_OPERANDS_PREROUNDED
+    return p
+
+
 def test_backward_argument_validation():
     L = hk.lib()
     assert L.hk_attn_backward(None, None) == -1
     p = BP()
     assert L.hk_attn_backward(C.byref(p), None) == -1
     assert L.hk_attn_bwd_precompute_D(C.byref(p), None) == -1
+    p = _bwd_block(); p.scale = 0.0
+    assert L.hk_attn_backward(C.byref(p), None) == -2         # the same scale rule as the forward
+    p = _fwd_block(); p.scale = 0.0
+    assert L.hk_attn_forward(C.byref(p), None) == -2
+    p = _bwd_block(); p.dq_strideM = 32
+    assert L.hk_attn_backward(C.byref(p), None) == -2         # rows would overlap
+    p = _bwd_block(); p.do_strideM = 32
+    assert L.hk_attn_bwd_precompute_D(C.byref(p), None) == -2
+    p = _bwd_block(); p.do_strideM = 32
+    assert L.hk_attn_bwd_precompute_D_hd(C.byref(p), 64, None) == -2
+    assert L.hk_attn_bwd_precompute_D_hd(C.byref(_bwd_block()), 72, None) == -6   # not one of the reference's ten
+
+
+def test_broadcast_strides_are_refused():
+    """A zero batch/head stride cannot be expressed by the TMA tensor maps: refused up front, not as a CUDA error."""
+    L = hk.lib()
+    p = _fwd_block(); p.nh = 4; p.k_strideH = 0
+    assert L.hk_attn_forward(C.byref(p), None) == -6
+    p = _fwd_block(); p.B = 2; p.v_strideB = 0
+    assert L.hk_attn_forward(C.byref(p), None) == -6
+    p = _bwd_block(); p.nh = 2; p.dk_strideH = 0
+    assert L.hk_attn_backward(C.byref(p), None) == -6
+    p = _fwd_block(); p.k_strideH = 0          # a single head may carry any stride
+    assert L.hk_attn_forward(C.byref(p), None) != -6
 
 
 def test_workspace_sizes():
@@ -107,6 +144,14 @@ def test_host_mask_twin_matches_oracle():
     a = hk.dropout_keep_mask(2, 33, 70, 0.1, seed=42, offset=3, q_pos0=5, k_pos0=8)
     b = ol.dropout_mask(2, 33, 70, 0.1, 42, 3, 5, 8)
     assert np.array_equal(a, b)
+
+
+def test_host_mask_twin_of_a_run_of_slices():
+    """bh_pos0: the mask of (batch, head) slices 3..4 of a larger problem is rows 3..4 of the whole mask."""
+    whole = hk.dropout_keep_mask(6, 17, 40, 0.3, seed=7, offset=1 << 33)
+    part = hk.dropout_keep_mask(2, 17, 40, 0.3, seed=7, offset=1 << 33, bh_pos0=3)
+    assert np.array_equal(part, whole[3:5])
+    assert not np.array_equal(part, whole[0:2])
 
 
 def test_missing_library_fails_loudly(monkeypatch):

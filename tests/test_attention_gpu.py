@@ -185,13 +185,13 @@ def _philox_mask_numpy(bh, Tq, Tk, p, seed, offset, q_pos0=0, k_pos0=0):
 
 
 def test_config3_noncausal_dropout_subset():
-    """B=16,H=16,N=2048, p=0.1, sigma 0.5; 4 heads against the oracle, incl. first and last."""
-    _subset_check(16, 16, 2048, 0, 0.1, 0.5, [(0, 0), (7, 3), (15, 15), (3, 9)], seed=3)
+    """B=16,H=16,N=2048, p=0.1, sigma 0.5; 8 heads against the oracle, incl. first and last."""
+    _subset_check(16, 16, 2048, 0, 0.1, 0.5, [(0, 0), (7, 3), (15, 15), (3, 9), (0, 15), (15, 0), (8, 8), (11, 5)], seed=3)
 
 
 def test_config4_gpt2_xl_causal_dropout_subset():
-    """B=32,H=25,N=1024 causal p=0.1; 6 heads against the oracle."""
-    _subset_check(32, 25, 1024, 1, 0.1, 1.0, [(0, 0), (31, 24), (5, 7), (16, 12), (1, 1), (20, 3)], seed=4)
+    """B=32,H=25,N=1024 causal p=0.1; 8 heads against the oracle, incl. first and last."""
+    _subset_check(32, 25, 1024, 1, 0.1, 1.0, [(0, 0), (31, 24), (5, 7), (16, 12), (1, 1), (20, 3), (0, 24), (31, 0)], seed=4)
 
 
 # ---------------------------------------------------------------------------
@@ -415,7 +415,7 @@ def test_precompute_D_reference_shape():
     assert ol.max_abs(host(D), ol.precompute_D(dO, O)) <= 1e-4
 
 
-@pytest.mark.parametrize("hd", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("hd", [16, 32, 48, 64, 80, 96, 128, 160, 192, 256])
 def test_precompute_D_other_head_dims(hd):
     """mem_efficient_bwd_precompute_D_sm89.cu:93-102 instantiates the pre-pass for these head dimensions; rows of a
     [B, T, H, hd] layout (strided heads) and a ragged row count."""
@@ -436,7 +436,7 @@ def test_precompute_D_other_head_dims(hd):
     ref = (dO.astype(np.float64) * O).sum(-1).transpose(0, 2, 1)
     assert np.abs(host(D) - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
     with pytest.raises(hk.HKError):
-        hk.mem_efficient_bwd_precompute_D(p, head_dim=48)
+        hk.mem_efficient_bwd_precompute_D(p, head_dim=72)  # not one of the reference's ten instantiations
 
 
 def test_backward_with_precomputed_D_and_accumulation():
@@ -492,6 +492,51 @@ def test_host_step_pipeline_matches_direct_calls(chunks):
     assert torch.equal(hdK, dK.cpu()) and torch.equal(hdV, dV.cpu())
     assert float((hdQ - dQ.cpu()).abs().max()) <= 1e-4
     assert hs.h2d_bytes == 4 * Q.nbytes and hs.d2h_bytes == 4 * Q.nbytes + LSE.numel() * 4
+
+
+@pytest.mark.parametrize("chunks", [2, 4])
+def test_host_step_with_dropout_draws_the_mask_of_the_single_call(chunks):
+    """Philox dropout through HostAttentionStep: every chunk passes the index of its first (batch, head) slice
+    (bh_pos0) with the same seed and offset, so the chunked step reproduces the direct call over the whole batch
+    bit for bit on O, LSE, dK, dV (dQ up to the order of its fp32 reductions)."""
+    B, H, T, p, seed, off = 4, 3, 384, 0.1, 0xABCDEF0123, 5
+    Q, K, V, dO = (normal((B, H, T, 64), 180 + s) for s in range(4))
+    tQ, tK, tV, tdO = dev(Q), dev(K), dev(V), dev(dO)
+    kw = dict(dropout_p=p, philox_seed=seed, philox_offset=off)
+    O, LSE = hk.attention_forward(tQ, tK, tV, SCALE, 1, **kw)
+    dQ, dK, dV, _ = hk.attention_backward(tQ, tK, tV, O, tdO, LSE, SCALE, 1, **kw)
+    hin = [torch.from_numpy(x).pin_memory() for x in (Q, K, V, dO)]
+    hO, hdQ, hdK, hdV = (torch.full((B, H, T, 64), float("nan")).pin_memory() for _ in range(4))
+    hLSE = torch.full((B, H, T), float("nan")).pin_memory()
+    hs = hk.HostAttentionStep(B, H, T, SCALE, True, chunks=chunks, **kw)
+    hs.step(*hin, hO, hLSE, hdQ, hdK, hdV)
+    torch.cuda.synchronize()
+    ok_status()
+    assert torch.equal(hO, O.cpu()) and torch.equal(hLSE, LSE.cpu())
+    assert torch.equal(hdK, dK.cpu()) and torch.equal(hdV, dV.cpu())
+    assert float((hdQ - dQ.cpu()).abs().max()) <= 1e-4
+    # and the mask really is in play: without dropout the output differs
+    O0, _ = hk.attention_forward(tQ, tK, tV, SCALE, 1)
+    assert not torch.equal(O0, O)
+
+
+def test_batch_head_slices_reproduce_the_whole_call_under_dropout():
+    """A problem cut into runs of (batch, head) slices (what a batch x head partition over several GPUs does):
+    each run, called with bh_pos0 = its first slice, equals those slices of the single call, bit for bit."""
+    B, H, T, p, seed, off = 4, 5, 200, 0.2, 99, 3
+    Q, K, V, dO = (dev(normal((B, H, T, 64), 190 + s)) for s in range(4))
+    kw = dict(dropout_p=p, philox_seed=seed, philox_offset=off)
+    O, LSE = hk.attention_forward(Q, K, V, SCALE, 0, **kw)
+    dQ, dK, dV, _ = hk.attention_backward(Q, K, V, O, dO, LSE, SCALE, 0, **kw)
+    for b0, nb in ((0, 1), (1, 3)):
+        sl = slice(b0, b0 + nb)
+        q, k, v, g = (t[sl].contiguous() for t in (Q, K, V, dO))
+        o, l = hk.attention_forward(q, k, v, SCALE, 0, bh_pos0=b0 * H, **kw)
+        dq, dk, dv, _ = hk.attention_backward(q, k, v, o, g, l, SCALE, 0, bh_pos0=b0 * H, **kw)
+        assert torch.equal(o, O[sl]) and torch.equal(l, LSE[sl])
+        assert torch.equal(dk, dK[sl]) and torch.equal(dv, dV[sl])
+        assert float((dq - dQ[sl]).abs().max()) <= 1e-4
+    ok_status()
 
 
 def test_graphed_step_replays_the_direct_calls():
