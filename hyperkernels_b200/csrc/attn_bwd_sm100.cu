@@ -17,31 +17,42 @@
 // compute warps -- are directly the tensor-memory A operands of dV += P^T dO and
 // dK += dS^T Q.  dS is also staged once through shared memory (MN-major) as the
 // A operand of dQ = dS K.  dV, dK (64 columns each) stay in tensor memory for
-// the whole CTA; dQ (64 columns) is drained per query tile.  Everything the
-// kernel writes leaves through shared memory and the TMA unit: dQ tiles are
-// added to global memory with bulk reductions (per-thread atomics stall the
-// tensor-core instruction issue of the same SM), dV and dK are stored with bulk
-// copies at the end (a thread-per-row store touches 32 lines per instruction).
+// the whole CTA; dQ (64 columns) is drained per query tile; V (64 columns) is
+// copied into tensor memory once and is the A operand of dP^T, which frees its
+// 32 KiB of shared memory for dS.  Everything the kernel writes leaves through
+// shared memory and the TMA unit: dQ tiles are added to global memory with bulk
+// reductions (per-thread atomics stall the tensor-core instruction issue of the
+// same SM), dV and dK are stored with bulk copies at the end (a thread-per-row
+// store touches 32 lines per instruction).
 //
 // Q, dO and K each feed one product that contracts over d (K-major operand,
 // 16-byte-chunk swizzle) and one that contracts over the sequence (MN-major
-// operand, which for TF32 must use the 32-byte-chunk swizzle), so TMA brings
-// each of them into shared memory twice, once per swizzle.  The MN-major copies
-// of Q and dO are dead once dV and dK have consumed them, and dS is staged over
-// them for dQ = dS K; the K-major copies are free as soon as S^T and dP^T are
-// done, so the next query tile's are prefetched a whole tile ahead (dQ of the
-// previous tile passes through the K-major dO buffer first).
+// operand, which for TF32 must use the 32-byte-chunk swizzle; the tensor core
+// refuses the 32-byte-chunk swizzle for a K-major operand), so TMA brings each
+// of them into shared memory twice, once per swizzle.
 //
-// Tensor-pipe order per query tile i:  dV(i), dK(i) | S^T(i+1), dP^T(i+1) | dQ(i).
-// The compute warps start the exponentials of tile i+1 as soon as S^T(i+1) is
-// done, work on it while dP^T(i+1) and dQ(i) execute, and write dS(i) to shared
-// memory while S^T(i+1), dP^T(i+1) execute.
+// Tensor-pipe order per query tile i (one issuing warp):
+//     dV(i) | S^T(i+1) | dK(i) | dP^T(i+1)
+// with dQ(i) issued by a second warp as soon as dS(i) is staged.
+// S^T(i+1) only needs the P^T columns back, i.e. dV(i); issuing it before dK(i)
+// lets the compute warps start the exponentials of tile i+1 -- the longest
+// stretch of scalar work -- while dK(i), dP^T(i+1) and dQ(i) execute.  Two of the
+// four 32-column boxes of dS(i) go over the MN-major dO tile as soon as dV(i) has
+// consumed it; the other two have a buffer of their own, through which the
+// drained dQ(i-1) first leaves by bulk reduction.  No staging touches the K-major
+// Q and dO tiles, so their prefetch for tile i+1 starts as soon as S^T(i) and
+// dP^T(i) are done.  Measured tensor-pipe time of the 72 instructions of a tile:
+// about 3 050 cycles (M128 N128 K8: 74 cycles, M128 N64 K8: 36 from tensor
+// memory, 52 from shared memory).
 //
-//   warp 0     TMA producer (K, V once; Q and dO per query tile; dQ, dK, dV out)
-//   warp 1     MMA issuer
-//   warps 2-17 compute: four threads per key row (tensor-memory lane), each
-//              owning 32 of the 128 query columns, all held in registers so
-//              that S^T and dP^T are read from tensor memory exactly once
+//   warps 0-15  compute: four threads per key row (tensor-memory lane), each
+//               owning 32 of the 128 query columns, all held in registers so
+//               that S^T and dP^T are read from tensor memory exactly once
+//   warp 16     TMA loads (K, V once; Q and dO per query tile, each in two layouts)
+//   warp 17     MMA issuer of dV, S^T, dK, dP^T (the whole warp runs the issuing
+//               code, one elected lane issues)
+//   warp 18     MMA issuer of dQ
+//   warp 19     TMA reductions of dQ (per query tile) and stores of dK, dV (at the end)
 #include <mutex>
 
 #include "attn_kernels.cuh"
@@ -52,32 +63,42 @@ namespace hk {
 namespace bwd {
 
 constexpr int NUM_COMPUTE = 512;
-constexpr int NUM_THREADS = 64 + NUM_COMPUTE;
+constexpr int NUM_THREADS = NUM_COMPUTE + 128;  // 16 compute warps, 4 control warps
+constexpr int W_LOAD = 16, W_MMA = 17, W_MMA_DQ = 18, W_STORE = 19;
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0;     // S^T, then P^T
 constexpr int COL_DP = 128;  // dP^T, then dS^T
 constexpr int COL_DV = 256;
 constexpr int COL_DK = 320;
 constexpr int COL_DQ = 384;
+constexpr int COL_V = 448;   // V of this KV tile, A operand of dP^T
 
 struct __align__(16) Shared {
-    float lse[2][TILE];   // LSE * log2e of the query tile (+inf for rows past the end), double-buffered
-    float dsum[2][TILE];  // D * scale of the query tile
-    uint64_t k_full, v_full, km_full, q_full, do_full, qk_empty, qm_full, qm_free, s_full, dp_full, p_ready, b_done, ds_ready, dq_full, dq_empty, staged;
+    float lse[2][TILE];   // -LSE * log2e of the query tile (-inf for rows past the end), double-buffered
+    float dsum[2][TILE];  // -D * scale of the query tile
+    uint64_t k_full, v_full, km_full, q_full, do_full, qm_full, dom_full;  // TMA loads
+    uint64_t v_ready;       // V is in tensor memory (and its landing buffer is free)
+    uint64_t qk_free, dok_free;  // S^T(i) / dP^T(i) complete: the K-major Q / dO tile may be refilled
+    uint64_t s_full, dp_full;
+    uint64_t pt_ready;      // P^T is in tensor memory: dV += P^T dO (and then the next tile's S^T) may go
+    uint64_t p_ready;       // dS^T is in tensor memory too: dK += dS^T Q (and then the next tile's dP^T) may go
+    uint64_t dv_done, dk_done;   // dV(i) / dK(i) complete: the MN-major dO / Q tile is free
+    uint64_t ds_ready, dq_full, dq_empty, staged;
     uint64_t acc_staged;    // dV, dK of the CTA are staged for the bulk store
-    uint64_t dq_staged[2];  // dQ of a query tile is staged for the bulk reduction ([1]: the last tile, other buffer)
+    uint64_t dq_staged;     // dQ of a query tile is staged (in the K-major dO tile) for the bulk reduction
+    uint64_t dq_out;        // the bulk reduction has read the staged dQ tile: the K-major dO tile may be refilled
     uint32_t tmem_base;
     int abort_flag;
 };
 
-constexpr int OFF_KK = 0;                // K, K-major swizzle   (S^T = K Q^T)
+constexpr int OFF_KK = 0;                // K, K-major swizzle   (S^T = K Q^T); dK staging at the end
 constexpr int OFF_KM = TILE_BYTES;       // K, MN-major swizzle  (dQ = dS K)
-constexpr int OFF_V = 2 * TILE_BYTES;    // V, K-major           (dP^T = V dO^T)
-constexpr int OFF_QK = 3 * TILE_BYTES;   // Q, K-major           (S^T)
-constexpr int OFF_DOK = 4 * TILE_BYTES;  // dO, K-major          (dP^T)
-constexpr int OFF_QM = 5 * TILE_BYTES;   // Q, MN-major          (dK += dS^T Q)   } dS staging, 4 boxes of
-constexpr int OFF_DOM = 6 * TILE_BYTES;  // dO, MN-major         (dV += P^T dO)   } [128 kv][32 q], overlays these two
-constexpr int OFF_DS = OFF_QM;
+constexpr int OFF_QK = 2 * TILE_BYTES;   // Q, K-major           (S^T); staging of the last dQ
+constexpr int OFF_DOK = 3 * TILE_BYTES;  // dO, K-major          (dP^T)
+constexpr int OFF_QM = 4 * TILE_BYTES;   // Q, MN-major          (dK += dS^T Q); dV staging at the end
+constexpr int OFF_DOM = 5 * TILE_BYTES;  // dO, MN-major         (dV += P^T dO); dS boxes 0, 1 ([128 kv][32 q] each) once dV is done
+constexpr int OFF_DS = 6 * TILE_BYTES;   // dS boxes 2, 3; before them the dQ tile on its way out; first of all the landing buffer of V
+static_assert(OFF_DS == OFF_DOM + 2 * BOX_BYTES, "the four dS boxes are one descriptor: equally spaced");
 constexpr int OFF_SH = 7 * TILE_BYTES;
 // no slack for re-aligning the dynamic shared-memory base: it is declared 1024-byte aligned
 // and the kernel checks that it is (the 128-byte swizzles need it)
@@ -88,7 +109,7 @@ static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may opt in to");
 // buffer[1 + (it * 2 + r) * 8 + ph]; buffer[0] = number of iterations of the recorded CTA.
 #ifdef HK_TIMELINE
 __device__ __forceinline__ void stamp(const BwdArgs& a, bool on, int it, int role, int ph) {
-    if (on && it < 200) a.timeline[1 + (it * 2 + role) * 8 + ph] = clock64();
+    if (on && it < 80) a.timeline[1 + (it * 3 + role) * 16 + ph] = clock64();
 }
 #else
 __device__ __forceinline__ void stamp(const BwdArgs&, bool, int, int, int) {}
@@ -96,7 +117,7 @@ __device__ __forceinline__ void stamp(const BwdArgs&, bool, int, int, int) {}
 
 enum WaitId {
     W_KVFULL = 201, W_QKFULL, W_QKEMPTY, W_QMFULL, W_QMFREE, W_SFULL, W_PREADY, W_BDONE, W_DSREADY, W_DQFULL, W_DQEMPTY,
-    W_STAGED, W_DQSTAGED, W_ACCSTAGED
+    W_STAGED, W_DQSTAGED, W_ACCSTAGED, W_VREADY, W_DVDONE, W_DQOUT
 };
 
 }  // namespace bwd
@@ -118,7 +139,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #endif
     if (trace) {
         a.timeline[4 * blockIdx.x] = (long long)globaltimer_ns();
-        a.timeline[4 * blockIdx.x + 2] = smid();
+        a.timeline[4 * blockIdx.x + 2] = clock64();
     }
     if ((smem_u32(smem) & 1023u) != 0) {  // never expected; refuse to run on a misplaced buffer
         if (threadIdx.x == 0 && atomicCAS(&a.status->code, 0, 299) == 0) a.status->block = blockIdx.x;
@@ -126,12 +147,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
     uint8_t* sK = smem + OFF_KK;
     uint8_t* sKm = smem + OFF_KM;
-    uint8_t* sV = smem + OFF_V;
+    uint8_t* sV = smem + OFF_DS;  // landing buffer of V, read once into tensor memory
     uint8_t* sQ = smem + OFF_QK;
     uint8_t* sdO = smem + OFF_DOK;
     uint8_t* sQm = smem + OFF_QM;
     uint8_t* sdOm = smem + OFF_DOM;
-    uint8_t* sdS = smem + OFF_DS;
+    uint8_t* sdS = smem + OFF_DOM;  // box b at sdS + b * BOX_BYTES
     Shared& sh = *reinterpret_cast<Shared*>(smem + OFF_SH);
 
     const int warp = threadIdx.x >> 5;
@@ -159,24 +180,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         mbar_init(&sh.km_full, 1);
         mbar_init(&sh.q_full, 1);
         mbar_init(&sh.do_full, 1);
-        mbar_init(&sh.qk_empty, 1);
         mbar_init(&sh.qm_full, 1);
-        mbar_init(&sh.qm_free, 1);
+        mbar_init(&sh.dom_full, 1);
+        mbar_init(&sh.v_ready, NUM_COMPUTE);
+        mbar_init(&sh.qk_free, 1);
+        mbar_init(&sh.dok_free, 1);
         mbar_init(&sh.s_full, 1);
         mbar_init(&sh.dp_full, 1);
+        mbar_init(&sh.pt_ready, NUM_COMPUTE);
         mbar_init(&sh.p_ready, NUM_COMPUTE);
-        mbar_init(&sh.b_done, 1);
+        mbar_init(&sh.dv_done, 1);
+        mbar_init(&sh.dk_done, 1);
         mbar_init(&sh.ds_ready, NUM_COMPUTE);
         mbar_init(&sh.dq_full, 1);
-        mbar_init(&sh.dq_empty, 256);  // the two column groups that drain dQ
+        mbar_init(&sh.dq_empty, NUM_COMPUTE);
+        mbar_init(&sh.dq_staged, NUM_COMPUTE);
+        mbar_init(&sh.dq_out, 1);
         mbar_init(&sh.staged, 256);    // the threads that stage LSE and D
         mbar_init(&sh.acc_staged, NUM_COMPUTE);
-        mbar_init(&sh.dq_staged[0], 256);
-        mbar_init(&sh.dq_staged[1], 256);
         sh.abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 1) {
+    if (warp == W_MMA) {
         tmem_alloc(&sh.tmem_base, TMEM_COLS);
         tmem_relinquish();
         tc_fence_before_sync();
@@ -192,7 +217,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #endif
     if (tl && threadIdx.x == 0) a.timeline[0] = n_it;
 
-    if (warp == 0) {
+    if (warp == W_LOAD) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0 && n_it > 0) {
             tma_prefetch_desc(&mapQ);
@@ -202,11 +227,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tma_prefetch_desc(&mapQm);
             tma_prefetch_desc(&mapKm);
             tma_prefetch_desc(&mapdOm);
-            tma_prefetch_desc(&mapdQ);
-            tma_prefetch_desc(&mapdK);
-            tma_prefetch_desc(&mapdV);
-            // in the order the first products need them: K, Q (S^T), V, dO (dP^T), the MN-major Q, dO (dV, dK), K (dQ)
-            int issued_q = 0, issued_do = 0, issued_m = 0;
+            // in the order the first products need them: K, Q (S^T), V, dO (dP^T), MN-major dO (dV), Q (dK), K (dQ)
+            int issued_q = 0, issued_do = 0, issued_qm = 0, issued_dom = 0;
             auto load_q = [&](int q0) {
                 mbar_arrive_expect_tx(&sh.q_full, TILE_BYTES);
                 tma_load_4d(sQ, &mapQ, &sh.q_full, 0, q0, h, b);
@@ -220,25 +242,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 ++issued_do;
             };
             auto load_qm = [&](int q0) {
-                mbar_arrive_expect_tx(&sh.qm_full, 2 * TILE_BYTES);
+                mbar_arrive_expect_tx(&sh.qm_full, TILE_BYTES);
                 tma_load_4d(sQm, &mapQm, &sh.qm_full, 0, q0, h, b);
                 tma_load_4d(sQm + BOX_BYTES, &mapQm, &sh.qm_full, HALF_D, q0, h, b);
-                tma_load_4d(sdOm, &mapdOm, &sh.qm_full, 0, q0, h, b);
-                tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.qm_full, HALF_D, q0, h, b);
-                ++issued_m;
+                ++issued_qm;
             };
-            // dQ of query tile j, staged by the compute warps in the K-major dO tile (the K-major Q tile for the
-            // last one), which is idle between dP^T of one query tile and the prefetch of the next: add it to
-            // global memory
-            auto reduce_dq = [&](int j) -> bool {
-                const int last = (j == n_it - 1) ? 1 : 0;
-                if (!mbar_wait(wc, &sh.dq_staged[last], last ? 0 : (j & 1), W_DQSTAGED, j)) return false;
-                const uint8_t* src = last ? sQ : sdO;
-                const int q = (it0 + j) * TILE;
-                tma_reduce_add_4d(&mapdQ, src, 0, q, h, b);
-                tma_reduce_add_4d(&mapdQ, src + BOX_BYTES, HALF_D, q, h, b);
-                bulk_commit_group();
-                return true;
+            auto load_dom = [&](int q0) {
+                mbar_arrive_expect_tx(&sh.dom_full, TILE_BYTES);
+                tma_load_4d(sdOm, &mapdOm, &sh.dom_full, 0, q0, h, b);
+                tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.dom_full, HALF_D, q0, h, b);
+                ++issued_dom;
             };
             mbar_arrive_expect_tx(&sh.k_full, TILE_BYTES);
             tma_load_4d(sK, &mapK, &sh.k_full, 0, kv0, h, b);
@@ -248,6 +261,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tma_load_4d(sV, &mapV, &sh.v_full, 0, kv0, h, b);
             tma_load_4d(sV + BOX_BYTES, &mapV, &sh.v_full, HALF_D, kv0, h, b);
             load_do(it0 * TILE);
+            load_dom(it0 * TILE);
             load_qm(it0 * TILE);
             mbar_arrive_expect_tx(&sh.km_full, TILE_BYTES);
             tma_load_4d(sKm, &mapKm, &sh.km_full, 0, kv0, h, b);
@@ -255,122 +269,184 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             bool tok = true;
             for (int it = 0; it + 1 < n_it; ++it) {
                 const int q1 = (it0 + it + 1) * TILE;
-                // K-major Q, dO: free as soon as S^T(it), dP^T(it) are done ...
-                if (!(tok = mbar_wait(wc, &sh.qk_empty, it & 1, W_QKEMPTY, it))) break;
+                // K-major Q: free as soon as S^T(it) is done
+                if (!(tok = mbar_wait(wc, &sh.qk_free, it & 1, W_QKEMPTY, it))) break;
                 load_q(q1);
-                // ... but dQ(it-1) passes through the dO tile first
-                if (it > 0) {
-                    if (!(tok = reduce_dq(it - 1))) break;
-                    bulk_wait_group_read_all();
-                }
+                // K-major dO: dQ(it-1) passes through the tile once dP^T(it) is done; free when the reduction has read it
+                if (it == 0) {
+                    if (!(tok = mbar_wait(wc, &sh.dok_free, 0, W_QKEMPTY, 1000))) break;
+                } else if (!(tok = mbar_wait(wc, &sh.dq_out, (it - 1) & 1, W_DQOUT, it - 1))) break;
                 load_do(q1);
-                // MN-major Q, dO double as the dS staging area: free once dQ(it) is done
-                if (!(tok = mbar_wait(wc, &sh.qm_free, it & 1, W_QMFREE, it))) break;
+                // MN-major Q: free once dK(it) is done
+                if (!(tok = mbar_wait(wc, &sh.dk_done, it & 1, W_QMFREE, it))) break;
                 load_qm(q1);
+                // MN-major dO doubles as staging area of two dS boxes: free once dQ(it) is done
+                if (!(tok = mbar_wait(wc, &sh.dq_full, it & 1, W_QMFREE, 1000 + it))) break;
+                load_dom(q1);
             }
-            if (tok && n_it >= 2) tok = reduce_dq(n_it - 2);
-            // dV and dK, staged by the compute warps in the K-major V and K tiles (dead after the last S^T, dP^T):
-            // stored -- added, if the caller accumulates -- with bulk copies; a thread-per-row store would be
-            // 32 lines per instruction
-            if (tok && (tok = mbar_wait(wc, &sh.acc_staged, 0, W_ACCSTAGED, 0))) {
-                if (a.accum_dkdv) {
-                    tma_reduce_add_4d(&mapdV, sV, 0, kv0, h, b);
-                    tma_reduce_add_4d(&mapdV, sV + BOX_BYTES, HALF_D, kv0, h, b);
-                    tma_reduce_add_4d(&mapdK, sK, 0, kv0, h, b);
-                    tma_reduce_add_4d(&mapdK, sK + BOX_BYTES, HALF_D, kv0, h, b);
-                } else {
-                    tma_store_4d(&mapdV, sV, 0, kv0, h, b);
-                    tma_store_4d(&mapdV, sV + BOX_BYTES, HALF_D, kv0, h, b);
-                    tma_store_4d(&mapdK, sK, 0, kv0, h, b);
-                    tma_store_4d(&mapdK, sK + BOX_BYTES, HALF_D, kv0, h, b);
-                }
-                bulk_commit_group();
-            }
-            if (tok) tok = reduce_dq(n_it - 1);
-            bulk_wait_group_all();
             // Do not leave the CTA while bulk copies into its shared memory are in flight.
             for (int i = 0; i < 100000 && !mbar_try_wait(&sh.k_full, 0); ++i) {}
             for (int i = 0; i < 100000 && !mbar_try_wait(&sh.v_full, 0); ++i) {}
             for (int i = 0; i < 100000 && !mbar_try_wait(&sh.km_full, 0); ++i) {}
             for (int i = 0; i < 100000 && !mbar_try_wait(&sh.q_full, (issued_q - 1) & 1); ++i) {}
             for (int i = 0; i < 100000 && !mbar_try_wait(&sh.do_full, (issued_do - 1) & 1); ++i) {}
-            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.qm_full, (issued_m - 1) & 1); ++i) {}
+            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.qm_full, (issued_qm - 1) & 1); ++i) {}
+            for (int i = 0; i < 100000 && !mbar_try_wait(&sh.dom_full, (issued_dom - 1) & 1); ++i) {}
         }
-    } else if (warp == 1) {
+    } else if (warp == W_MMA) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0 && n_it > 0) {
+        // The whole warp runs this code with uniform control flow; only the tcgen05 instructions are predicated on
+        // the elected lane (see umma_ss_tf32_lead).
+        if (n_it > 0) {
+            const uint32_t leader = elect_one_sync();
+            auto wait = [&](uint64_t* bar, uint32_t parity, int id, int aux) -> bool {
+                return __all_sync(0xffffffffu, mbar_wait(wc, bar, parity, id, aux));
+            };
+            const bool tlm = tl && leader;
             constexpr uint32_t IDESC_ST = make_idesc_tf32(TILE, TILE, false, false);     // K-major x K-major, N = 128
             constexpr uint32_t IDESC_TS = make_idesc_tf32(TILE, HEAD_DIM, false, true);  // tmem A, MN-major B, N = 64
-            constexpr uint32_t IDESC_DQ = make_idesc_tf32(TILE, HEAD_DIM, true, true);   // MN-major A and B, N = 64
-            const uint32_t k_addr = smem_u32(sK), km_addr = smem_u32(sKm), v_addr = smem_u32(sV), q_addr = smem_u32(sQ),
-                           do_addr = smem_u32(sdO), qm_addr = smem_u32(sQm), dom_addr = smem_u32(sdOm),
-                           ds_addr = smem_u32(sdS);
-            // S^T and dP^T of query tile `it` (local index), each as soon as its own operands have landed
-            auto issue_a = [&](int it) -> bool {
-                if (it == 0 && !mbar_wait(wc, &sh.k_full, 0, W_KVFULL, 0)) return false;
-                if (!mbar_wait(wc, &sh.q_full, it & 1, W_QKFULL, it)) return false;
+            const uint32_t k_addr = smem_u32(sK), q_addr = smem_u32(sQ), do_addr = smem_u32(sdO), qm_addr = smem_u32(sQm),
+                           dom_addr = smem_u32(sdOm);
+            // S^T of query tile `it` (local index) as soon as K and Q have landed; the exponentials need nothing else
+            auto issue_st = [&](int it) -> bool {
+                if (it == 0 && !wait(&sh.k_full, 0, W_KVFULL, 0)) return false;
+                if (!wait(&sh.q_full, it & 1, W_QKFULL, it)) return false;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // S^T = K Q^T
-                    umma_ss_tf32(tmem + COL_S, kmajor_desc(k_addr, kk, BOX_BYTES), kmajor_desc(q_addr, kk, BOX_BYTES),
+                    umma_ss_tf32_lead(leader, tmem + COL_S, kmajor_desc(k_addr, kk, BOX_BYTES), kmajor_desc(q_addr, kk, BOX_BYTES),
                                  IDESC_ST, kk > 0);
-                umma_commit(&sh.s_full);  // the exponentials need S^T only
-                if (it == 0 && !mbar_wait(wc, &sh.v_full, 0, W_KVFULL, 1)) return false;
-                if (!mbar_wait(wc, &sh.do_full, it & 1, W_QKFULL, 1000 + it)) return false;
-                tc_fence_after_sync();
-#pragma unroll
-                for (int kk = 0; kk < HEAD_DIM / 8; ++kk)  // dP^T = V dO^T
-                    umma_ss_tf32(tmem + COL_DP, kmajor_desc(v_addr, kk, BOX_BYTES), kmajor_desc(do_addr, kk, BOX_BYTES),
-                                 IDESC_ST, kk > 0);
-                umma_commit(&sh.dp_full);
-                umma_commit(&sh.qk_empty);
+                umma_commit_lead(leader, &sh.s_full);
+                umma_commit_lead(leader, &sh.qk_free);
                 return true;
             };
-            bool ok = issue_a(0);
+            // dP^T = V dO^T, V from tensor memory
+            auto issue_dp = [&](int it) -> bool {
+                if (it == 0 && !wait(&sh.v_ready, 0, W_VREADY, 0)) return false;
+                if (!wait(&sh.do_full, it & 1, W_QKFULL, 1000 + it)) return false;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < HEAD_DIM / 8; ++kk)
+                    umma_ts_tf32_lead(leader, tmem + COL_DP, tmem + COL_V + kk * 8, kmajor_desc(do_addr, kk, BOX_BYTES), IDESC_ST, kk > 0);
+                umma_commit_lead(leader, &sh.dp_full);
+                umma_commit_lead(leader, &sh.dok_free);
+                return true;
+            };
+            bool ok = issue_st(0) && issue_dp(0);
             for (int it = 0; ok && it < n_it; ++it) {
                 const uint32_t par = it & 1;
-                stamp(a, tl, it, 0, 0);
-                if (!(ok = mbar_wait(wc, &sh.qm_full, par, W_QMFULL, it))) break;
-                if (!(ok = mbar_wait(wc, &sh.p_ready, par, W_PREADY, it))) break;
-                stamp(a, tl, it, 0, 1);
+                stamp(a, tlm, it, 0, 0);
+                if (!(ok = wait(&sh.dom_full, par, W_QMFULL, it))) break;
+                if (!(ok = wait(&sh.pt_ready, par, W_PREADY, it))) break;
+                stamp(a, tlm, it, 0, 1);
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < TILE / 8; ++kk)  // dV += P^T dO
-                    umma_ts_tf32(tmem + COL_DV, tmem + COL_S + kk * 8, mnmajor_desc(dom_addr, kk, BOX_BYTES), IDESC_TS,
+                    umma_ts_tf32_lead(leader, tmem + COL_DV, tmem + COL_S + kk * 8, mnmajor_desc(dom_addr, kk, BOX_BYTES), IDESC_TS,
                                  (it > 0 || kk > 0) ? 1u : 0u);
+                umma_commit_lead(leader, &sh.dv_done);  // MN-major dO consumed: two of the dS boxes may be staged over it
+                stamp(a, tlm, it, 0, 2);
+                // next tile's S^T: P^T of this tile was consumed by the MMAs just issued
+                if (it + 1 < n_it && !(ok = issue_st(it + 1))) break;
+                stamp(a, tlm, it, 0, 3);
+                if (!(ok = wait(&sh.qm_full, par, W_QMFULL, 1000 + it))) break;
+                if (!(ok = wait(&sh.p_ready, par, W_PREADY, 1000 + it))) break;
+                tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < TILE / 8; ++kk)  // dK += dS^T Q
-                    umma_ts_tf32(tmem + COL_DK, tmem + COL_DP + kk * 8, mnmajor_desc(qm_addr, kk, BOX_BYTES), IDESC_TS,
+                    umma_ts_tf32_lead(leader, tmem + COL_DK, tmem + COL_DP + kk * 8, mnmajor_desc(qm_addr, kk, BOX_BYTES), IDESC_TS,
                                  (it > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&sh.b_done);  // MN-major Q, dO consumed: the compute warps may stage dS over them
-                stamp(a, tl, it, 0, 2);
-                if (it + 1 < n_it) {
-                    // next tile's S^T, dP^T: P^T and dS^T of this tile were consumed by the MMAs just issued
-                    stamp(a, tl, it, 0, 3);
-                    if (!(ok = issue_a(it + 1))) break;
-                    stamp(a, tl, it, 0, 4);
+                umma_commit_lead(leader, &sh.dk_done);  // MN-major Q consumed
+                // next tile's dP^T: dS^T of this tile was consumed by the MMAs just issued
+                if (it + 1 < n_it && !(ok = issue_dp(it + 1))) break;
+                stamp(a, tlm, it, 0, 4);
+                stamp(a, tlm, it, 0, 7);
+            }
+        }
+    } else if (warp == W_STORE) {
+#ifdef HK_TIMELINE
+        // completion monitor (development builds): when each product of a tile is done
+        if (lane == 1 && tl) {
+            bool mok = true;
+            for (int it = 0; mok && it < n_it; ++it) {
+                if ((mok = mbar_wait(wc, &sh.dv_done, it & 1, 990, it))) stamp(a, true, it, 2, 0);
+                if (mok && it + 1 < n_it && (mok = mbar_wait(wc, &sh.s_full, (it + 1) & 1, 991, it))) stamp(a, true, it, 2, 1);
+                if (mok && (mok = mbar_wait(wc, &sh.dk_done, it & 1, 992, it))) stamp(a, true, it, 2, 2);
+                if (mok && it + 1 < n_it && (mok = mbar_wait(wc, &sh.dp_full, (it + 1) & 1, 993, it))) stamp(a, true, it, 2, 3);
+                if (mok && (mok = mbar_wait(wc, &sh.dq_full, it & 1, 994, it))) stamp(a, true, it, 2, 4);
+            }
+        }
+#endif
+        // ------------------------------ store warp ------------------------------
+        // Everything that leaves the CTA: the staged dQ tiles (bulk reductions) and, at the end, dV and dK (bulk
+        // stores).  A thread of its own, so that a reduction is issued the moment its tile is staged.
+        if (lane == 0 && n_it > 0) {
+            tma_prefetch_desc(&mapdK);
+            tma_prefetch_desc(&mapdV);
+            tma_prefetch_desc(&mapdQ);
+            // dQ of query tile j, staged in the K-major dO tile: add it to global memory; once the reduction has read
+            // the tile, hand it back to the load warp
+            auto reduce_dq = [&](int j) -> bool {
+                if (!mbar_wait(wc, &sh.dq_staged, j & 1, W_DQSTAGED, j)) return false;
+                const int q = (it0 + j) * TILE;
+                tma_reduce_add_4d(&mapdQ, sdO, 0, q, h, b);
+                tma_reduce_add_4d(&mapdQ, sdO + BOX_BYTES, HALF_D, q, h, b);
+                bulk_commit_group();
+                bulk_wait_group_read_all();
+                mbar_arrive(&sh.dq_out);
+                return true;
+            };
+            bool tok = true;
+            for (int j = 0; tok && j + 1 < n_it; ++j) tok = reduce_dq(j);  // the last tile's dQ leaves from registers
+            // dV and dK, staged by the compute warps in the MN-major Q tile and the K-major K tile (dead after the last
+            // dK and S^T): stored -- added, if the caller accumulates -- with bulk copies; a thread-per-row store would
+            // be 32 lines per instruction
+            if (tok && (tok = mbar_wait(wc, &sh.acc_staged, 0, W_ACCSTAGED, 0))) {
+                if (a.accum_dkdv) {
+                    tma_reduce_add_4d(&mapdV, sQm, 0, kv0, h, b);
+                    tma_reduce_add_4d(&mapdV, sQm + BOX_BYTES, HALF_D, kv0, h, b);
+                    tma_reduce_add_4d(&mapdK, sK, 0, kv0, h, b);
+                    tma_reduce_add_4d(&mapdK, sK + BOX_BYTES, HALF_D, kv0, h, b);
+                } else {
+                    tma_store_4d(&mapdV, sQm, 0, kv0, h, b);
+                    tma_store_4d(&mapdV, sQm + BOX_BYTES, HALF_D, kv0, h, b);
+                    tma_store_4d(&mapdK, sK, 0, kv0, h, b);
+                    tma_store_4d(&mapdK, sK + BOX_BYTES, HALF_D, kv0, h, b);
                 }
-                if (!(ok = mbar_wait(wc, &sh.ds_ready, par, W_DSREADY, it))) break;
-                stamp(a, tl, it, 0, 5);
-                if (it > 0 && !(ok = mbar_wait(wc, &sh.dq_empty, (it - 1) & 1, W_DQEMPTY, it))) break;
-                if (it == 0 && !(ok = mbar_wait(wc, &sh.km_full, 0, W_KVFULL, 2))) break;
-                stamp(a, tl, it, 0, 6);
+                bulk_commit_group();
+            }
+            // the copies have read their shared-memory sources; they complete on their own
+            bulk_wait_group_read_all();
+        }
+    } else if (warp == W_MMA_DQ) {
+        // ------------------------------ dQ issuer ------------------------------
+        // dQ(i) = dS(i) K goes as soon as dS(i) is staged, whatever the other issuing warp is doing: the tensor pipe
+        // takes instructions from both, and nothing orders dQ(i) against dK(i), S^T(i+1) or dP^T(i+1).
+        if (n_it > 0) {
+            const uint32_t leader = elect_one_sync();
+            auto wait = [&](uint64_t* bar, uint32_t parity, int id, int aux) -> bool {
+                return __all_sync(0xffffffffu, mbar_wait(wc, bar, parity, id, aux));
+            };
+            constexpr uint32_t IDESC_DQ = make_idesc_tf32(TILE, HEAD_DIM, true, true);   // MN-major A and B, N = 64
+            const uint32_t km_addr = smem_u32(sKm), ds_addr = smem_u32(sdS);
+            bool ok = wait(&sh.km_full, 0, W_KVFULL, 2);
+            for (int it = 0; ok && it < n_it; ++it) {
+                if (!(ok = wait(&sh.ds_ready, it & 1, W_DSREADY, it))) break;
+                if (it > 0 && !(ok = wait(&sh.dq_empty, (it - 1) & 1, W_DQEMPTY, it))) break;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < TILE / 8; ++kk)  // dQ = dS K
-                    umma_ss_tf32(tmem + COL_DQ, mnmajor_desc(ds_addr, kk, BOX_BYTES), mnmajor_desc(km_addr, kk, BOX_BYTES),
-                                 IDESC_DQ, kk > 0);
-                umma_commit(&sh.qm_free);
-                umma_commit(&sh.dq_full);
-                stamp(a, tl, it, 0, 7);
+                    umma_ss_tf32_lead(leader, tmem + COL_DQ, mnmajor_desc(ds_addr, kk, BOX_BYTES),
+                                      mnmajor_desc(km_addr, kk, BOX_BYTES), IDESC_DQ, kk > 0);
+                umma_commit_lead(leader, &sh.dq_full);  // also: the dS staging area is free again
             }
         }
     } else {
         // ------------------------------ compute ------------------------------
         const int quarter = warp & 3;
-        const int part = (warp - 2) >> 2;       // which 32 of the 128 query columns this thread owns
+        const int part = warp >> 2;             // which 32 of the 128 query columns this thread owns
         const int row = quarter * 32 + lane;    // key row inside the tile = tensor-memory lane
-        const int tid = threadIdx.x - 64;       // 0..511 among the compute warps
+        const int tid = threadIdx.x;            // 0..511: the compute warps come first
         const int c0 = part * 32;
         const int kvrow = kv0 + row;
         const bool kv_ok = kvrow < a.Tk;
@@ -379,36 +455,66 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         const float* d_bh = a.D + (int64_t)b * a.d_sB + (int64_t)h * a.d_sH;
         bool ok = true;
         uint32_t rs[32], rp[32];
-        const bool tlc = tl && tid == 0;
-        // dQ of query tile j (this thread: query row `row`, columns 32*part..) into the staging buffer in the
-        // layout of a 128-byte-swizzled TMA box: 16-byte chunk c of row r at chunk position c ^ (r & 7).
-        // The buffer is free: dq_full(j) implies that S^T/dP^T of tile j+1, its last readers, are complete,
-        // and the producer refills it only after the reduction has read it.
-        auto stage_dq = [&](int j, const uint32_t* v) {
-            const int last = (j == n_it - 1) ? 1 : 0;
-            uint8_t* srow = (last ? sQ : sdO) + part * BOX_BYTES + row * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) =
-                    make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-            fence_proxy_async_smem();
-            mbar_arrive(&sh.dq_staged[last]);
-        };
-
-        // LSE * log2e (threads 0..127; +inf past the end and for a fully dropped row, so that every p is 0) or
-        // D * scale (threads 128..255) of query row q0 + (tid & 127)
+#ifndef HK_TL_TID
+#define HK_TL_TID 0  // compute thread whose phases a -DHK_TIMELINE build records
+#endif
+        const bool tlc = tl && tid == HK_TL_TID;
+        // -LSE * log2e (threads 0..127; -inf past the end and for a fully dropped row, so that every p is 0) or
+        // -D * scale (threads 128..255) of query row q0 + (tid & 127): negated, so that both enter as FMA addends
         auto fetch_lse_or_d = [&](int q0) -> float {
             const int q = q0 + (tid & 127);
             if (tid < TILE) {
-                if (q >= a.Tq) return INFINITY;
+                if (q >= a.Tq) return -INFINITY;
                 const float l = __ldg(lse_bh + q);
-                return (l == -INFINITY) ? INFINITY : l * LOG2E;
+                return (l == -INFINITY) ? -INFINITY : -l * LOG2E;
             }
-            return (q < a.Tq) ? __ldg(d_bh + q) * a.scale : 0.f;
+            return (q < a.Tq) ? -__ldg(d_bh + q) * a.scale : 0.f;
         };
         float staged_val = (tid < 2 * TILE && n_it > 0) ? fetch_lse_or_d(it0 * TILE) : 0.f;
 
-        for (int it = 0; it < n_it; ++it) {
+        // dQ of query tile j out of tensor memory into the K-major dO tile (this thread: query row `row`, columns
+        // 16*part..16*part+15), in the layout of a 128-byte-swizzled TMA box: 16-byte chunk c of row r at position
+        // c ^ (r & 7).  Called between the two halves of the NEXT tile's compute, when dP^T of that tile is done: its
+        // operand, the K-major dO tile, is then dead until the tile after it is prefetched, long enough for the bulk
+        // reduction, which keeps its source for ~1 600 cycles.
+        auto drain_dq = [&](int j) -> bool {
+            if (!__all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, j & 1, W_DQFULL, j))) return false;
+            tc_fence_after_sync();
+            uint32_t v[16];
+            tmem_ld16(trow + COL_DQ + 16 * part, v);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive(&sh.dq_empty);  // dQ is in registers: the next dQ = dS K may overwrite tensor memory
+            uint8_t* srow = sdO + (part >> 1) * BOX_BYTES + row * 128;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(srow + (((4 * (part & 1) + c) ^ (row & 7)) << 4)) =
+                    make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+            fence_proxy_async_smem();
+            mbar_arrive(&sh.dq_staged);
+            return true;
+        };
+
+        // V of this KV tile into tensor memory (A operand of dP^T = V dO^T): this thread's key row, 16 of the 64
+        // columns, read from the 128-byte-swizzled landing buffer (16-byte chunk c of row r at position c ^ (r & 7))
+        if (n_it > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.v_full, 0, W_KVFULL, 3));
+            if (ok) {
+                uint32_t rv[16];
+                const uint8_t* vrow = sV + (part >> 1) * BOX_BYTES + row * 128;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 x = *reinterpret_cast<const uint4*>(vrow + (((4 * (part & 1) + c) ^ (row & 7)) << 4));
+                    rv[4 * c] = x.x; rv[4 * c + 1] = x.y; rv[4 * c + 2] = x.z; rv[4 * c + 3] = x.w;
+                }
+                tmem_st16(trow + COL_V + 16 * part, rv);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sh.v_ready);
+            }
+        }
+
+        for (int it = 0; ok && it < n_it; ++it) {
             const int q0 = (it0 + it) * TILE;
             stamp(a, tlc, it, 1, 0);
             // stage LSE (threads 0..127) and D (threads 128..255) of this query tile into buffer it & 1.
@@ -435,6 +541,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tc_fence_after_sync();
 
             tmem_ld32(trow + COL_S + c0, rs);
+            stamp(a, tlc, it, 1, 8);
 
             // first query column (local to the tile) this key row is visible to
             int cmin = 0;
@@ -487,19 +594,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             // pairs whose p is zero: hidden ones, and dropped ones unless the dropout is the inverted kind
             const uint32_t live = a.drop_scaled ? vis : keep;
             tmem_wait_ld();
+            stamp(a, tlc, it, 1, 9);
 
-            // p = exp2(s*scale*log2e - LSE*log2e) needs S^T only: dP^T is still being computed
+            // p = exp2(s*scale*log2e - LSE*log2e) needs S^T only: dP^T is still being computed.  Two scores per
+            // packed FMA (fma.rn.f32x2 gives the same bits as two scalar FMAs).
             {
                 const float4* lse4 = reinterpret_cast<const float4*>(sh.lse[it & 1] + c0);
+                const float2 c2 = make_float2(a.scale_log2e, a.scale_log2e);
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     const float4 L = lse4[g];
-                    const float Ls[4] = {L.x, L.y, L.z, L.w};
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        const int i = g * 4 + t;
-                        rs[i] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(rs[i]), a.scale_log2e, -Ls[t])));
-                    }
+                    const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(rs[4 * g]), __uint_as_float(rs[4 * g + 1])), c2,
+                                                  make_float2(L.x, L.y));
+                    const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(rs[4 * g + 2]), __uint_as_float(rs[4 * g + 3])), c2,
+                                                  make_float2(L.z, L.w));
+                    rs[4 * g] = __float_as_uint(ex2_approx(x01.x));
+                    rs[4 * g + 1] = __float_as_uint(ex2_approx(x01.y));
+                    rs[4 * g + 2] = __float_as_uint(ex2_approx(x23.x));
+                    rs[4 * g + 3] = __float_as_uint(ex2_approx(x23.y));
                 }
                 if (live != 0xffffffffu) {  // tiles on the diagonal, the ragged end, dropout
 #pragma unroll
@@ -507,67 +619,79 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                         if (!((live >> i) & 1u)) rs[i] = 0u;
                 }
             }
+            stamp(a, tlc, it, 1, 10);
+            // P^T goes to tensor memory at once (rounded; a pair dropped by inverted dropout counts as zero in dV but
+            // keeps its p for dS below): dV += P^T dO and, behind it, the next tile's S^T run while dS is computed,
+            // and the store has drained by the time its first reader starts.  rp is free until dP^T is loaded.
+            {
+                const bool dropped_some = a.drop_scaled && keep != 0xffffffffu;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) rp[i] = tf32_round_bits_mma(rs[i]);
+                if (dropped_some) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (!((keep >> i) & 1u)) rp[i] = 0u;
+                }
+                tmem_st32(trow + COL_S + c0, rp);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&sh.pt_ready);
+            }
             ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dp_full, it & 1, W_SFULL, 1000 + it));
             if (!ok) break;
+            stamp(a, tlc, it, 1, 11);
             tc_fence_after_sync();
             tmem_ld32(trow + COL_DP + c0, rp);
+            if (it > 0 && !(ok = drain_dq(it - 1))) break;  // while the load is in flight
             tmem_wait_ld();
             stamp(a, tlc, it, 1, 3);
 
-            // dS = p * (dP*scale - D*scale)
+            // dS = p * (dP*scale - D*scale), two elements per packed instruction
             {
                 const float4* ds4 = reinterpret_cast<const float4*>(sh.dsum[it & 1] + c0);
                 const bool dropped_some = a.drop_scaled && keep != 0xffffffffu;
                 if (dropped_some) {
                     // inverted dropout: a dropped pair keeps the -D term of dS but contributes neither dP (zeroed
-                    // here) nor to dV (its P^T entry is zeroed below, after dS has been formed)
+                    // here) nor to dV (its P^T entry was stored as zero above)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         if (!((keep >> i) & 1u)) rp[i] = 0u;
                 }
+                const float2 dps2 = make_float2(a.dp_scale, a.dp_scale);
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
-                    const float4 Dv = ds4[g];
-                    const float Ds[4] = {Dv.x, Dv.y, Dv.z, Dv.w};
+                    const float4 Dv = ds4[g];  // -D * scale
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        const int i = g * 4 + t;
-                        const float ds = __uint_as_float(rs[i]) * fmaf(__uint_as_float(rp[i]), a.dp_scale, -Ds[t]);
-                        rs[i] = tf32_round_bits_mma(rs[i]);
-                        rp[i] = tf32_round_bits_mma(__float_as_uint(ds));
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const int i = 4 * g + 2 * h2;
+                        const float2 nd = h2 ? make_float2(Dv.z, Dv.w) : make_float2(Dv.x, Dv.y);
+                        const float2 t = __ffma2_rn(make_float2(__uint_as_float(rp[i]), __uint_as_float(rp[i + 1])), dps2, nd);
+                        const float2 ds = __fmul2_rn(make_float2(__uint_as_float(rs[i]), __uint_as_float(rs[i + 1])), t);
+                        rp[i] = tf32_round_bits_mma(__float_as_uint(ds.x));
+                        rp[i + 1] = tf32_round_bits_mma(__float_as_uint(ds.y));
                     }
-                }
-                if (dropped_some) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (!((keep >> i) & 1u)) rs[i] = 0u;
                 }
             }
             stamp(a, tlc, it, 1, 4);
-            tmem_st32(trow + COL_S + c0, rs);
             tmem_st32(trow + COL_DP + c0, rp);
+            stamp(a, tlc, it, 1, 12);
             tmem_wait_st();
+            stamp(a, tlc, it, 1, 13);
             tc_fence_before_sync();
-            mbar_arrive(&sh.p_ready);  // dV += P^T dO and dK += dS^T Q may go
+            mbar_arrive(&sh.p_ready);  // dK += dS^T Q may go
             stamp(a, tlc, it, 1, 5);
 
-            // drain dQ of the PREVIOUS query tile (lane = query row; column groups 0 and 1 take 32 columns
-            // each): its dQ = dS K was issued behind this tile's S^T, dP^T and has had this tile's compute to finish
-            if (it > 0 && part < 2) {
-                ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (it - 1) & 1, W_DQFULL, it - 1));
-                if (!ok) break;
-                tc_fence_after_sync();
-                tmem_ld32(trow + COL_DQ + part * 32, rs);
-                tmem_wait_ld();
-                tc_fence_before_sync();
-                mbar_arrive(&sh.dq_empty);  // dQ is in registers: the next dQ = dS K may overwrite tensor memory
-                stage_dq(it - 1, rs);
+            // dS into shared memory, the MN-major A operand of dQ = dS K: box `part` holds query columns
+            // 32*part..32*part+31, one 128-byte row per key row, 32-byte chunks XOR-swizzled with (row & 3).  Boxes 2, 3
+            // have a buffer of their own, free once dQ of the previous tile is done (before the first tile it held V,
+            // which every thread has left once v_ready completes); boxes 0, 1 go over the MN-major dO tile as soon as
+            // dV of this tile is done.
+            if (part >= 2) {
+                // dQ of the previous tile is done: every thread waited for it when it drained that tile
+                if (it == 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.v_ready, 0, W_VREADY, 1));
+            } else {
+                ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dv_done, it & 1, W_DVDONE, it));
             }
-
-            // dS into shared memory (MN-major A operand of dQ = dS K), over the MN-major Q/dO copies once dV/dK
-            // have consumed them: box `part` holds query columns 32*part..32*part+31, one 128-byte row per key
-            // row, 32-byte chunks XOR-swizzled with (row & 3)
-            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.b_done, it & 1, W_BDONE, it));
             if (!ok) break;
             stamp(a, tlc, it, 1, 6);
             {
@@ -589,15 +713,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             stamp(a, tlc, it, 1, 7);
         }
 
-        // dV and dK of this KV tile are complete (b_done of the last query tile covered every product into them).
-        // Column groups 0,1 put dV (times 1/(1-p) for inverted dropout) and groups 2,3 dK into the K-major V and K
-        // buffers, as the boxes of a 128-byte-swizzled TMA tile: 16-byte chunk c of row r at position c ^ (r & 7).
+        // dV and dK of this KV tile are complete once dK of the last query tile is (dV precedes it on the tensor
+        // pipe).  Column groups 0,1 put dV (times 1/(1-p) for inverted dropout) into the MN-major Q tile and groups
+        // 2,3 dK into the K-major K tile, both dead by then, as the boxes of a 128-byte-swizzled TMA tile: 16-byte
+        // chunk c of row r at position c ^ (r & 7).
+        if (ok && n_it > 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dk_done, (n_it - 1) & 1, W_BDONE, n_it));
         if (ok && n_it > 0) {
             tc_fence_after_sync();
             tmem_ld32(trow + ((part < 2) ? COL_DV + part * 32 : COL_DK + (part - 2) * 32), rs);
             tmem_wait_ld();
             const float f = (part < 2) ? a.dv_scale : 1.f;
-            uint8_t* srow = ((part < 2) ? sV : sK) + (part & 1) * BOX_BYTES + row * 128;
+            uint8_t* srow = ((part < 2) ? sQm : sK) + (part & 1) * BOX_BYTES + row * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<float4*>(srow + ((c ^ (row & 7)) << 4)) =
@@ -614,28 +740,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(out_row + i) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
 
-        // dQ of the last query tile
-        if (ok && n_it > 0 && part < 2) {
+        // dQ of the last query tile: nothing is left to overlap a bulk reduction with (it keeps its shared-memory
+        // source for ~1 600 cycles, and the CTA could not end before), so it goes from tensor memory to global memory
+        // through registers, in the accumulator-fragment shape (four threads hold 32 consecutive bytes of a row):
+        // column group 2 takes the first 16 lanes of its warp's quarter, group 3 the other 16.  The additions
+        // complete on their own after the CTA has gone.
+        if (ok && n_it > 0 && part >= 2) {
             ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (n_it - 1) & 1, W_DQFULL, n_it - 1));
             if (ok) {
                 tc_fence_after_sync();
-                tmem_ld32(trow + COL_DQ + part * 32, rs);
+                tmem_ld_16x256b_x8(tmem + ((uint32_t)(quarter * 32 + 16 * (part & 1)) << 16) + COL_DQ, rs);
                 tmem_wait_ld();
-                stage_dq(n_it - 1, rs);
+                const int q0j = (it0 + n_it - 1) * TILE;
+                const int ra = quarter * 32 + 16 * (part & 1) + (lane >> 2);
+                float* gA = a.dQ + (int64_t)b * a.dq_sB + (int64_t)h * a.dq_sH + (int64_t)(q0j + ra) * a.dq_sM + 2 * (lane & 3);
+                float* gB = gA + 8 * a.dq_sM;
+                const bool okA = q0j + ra < a.Tq, okB = q0j + ra + 8 < a.Tq;
+#pragma unroll
+                for (int jg = 0; jg < 8; ++jg) {
+                    if (okA) red_add_v2(gA + 8 * jg, rs[4 * jg], rs[4 * jg + 1]);
+                    if (okB) red_add_v2(gB + 8 * jg, rs[4 * jg + 2], rs[4 * jg + 3]);
+                }
             }
         }
+
     }
 
     // ------------------------------ teardown ------------------------------
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == W_MMA) {
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem, TMEM_COLS);
     }
     if (trace) {
         a.timeline[4 * blockIdx.x + 1] = (long long)globaltimer_ns();
+        a.timeline[4 * blockIdx.x + 2] = smid() | ((clock64() - a.timeline[4 * blockIdx.x + 2]) << 10);  // SM id, SM cycles
         a.timeline[4 * blockIdx.x + 3] = n_it;
     }
 }

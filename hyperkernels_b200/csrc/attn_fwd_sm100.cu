@@ -15,7 +15,7 @@
 //                 two-stage ring (128-byte-swizzled boxes of 128 rows x 32
 //                 floats, mbarrier tx; V with the 32-byte-chunk swizzle an
 //                 MN-major TF32 operand needs).
-//   warp 1        MMA issuer, in the order PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1):
+//   warp 1        MMA issuer (the whole warp runs the issuing code, one elected lane issues), in the order PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1):
 //                 S_t = Q_t K^T is 8 tcgen05.mma (M128 N128 K8, operands from
 //                 shared memory), O_t += P_t V is 16 (M128 N64 K8, A = P_t read
 //                 from tensor memory, B = V MN-major from shared memory).
@@ -194,61 +194,68 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             }
         } else if (warp == 1) {
             // ------------------------------ MMA issuer ------------------------------
-            if (lane == 0 && n > 0) {
+            // The whole warp runs this code with uniform control flow; only the tcgen05 instructions are predicated
+            // on the elected lane (see umma_ss_tf32_lead).
+            if (n > 0) {
+                const uint32_t leader = elect_one_sync();
+                auto wait = [&](uint64_t* bar, uint32_t parity, int id, int aux) -> bool {
+                    return __all_sync(0xffffffffu, mbar_wait(wc, bar, parity, id, aux));
+                };
+                const bool tlm = tl && leader;
                 constexpr uint32_t IDESC_S = make_idesc_tf32(TILE, TILE, false, false);
                 constexpr uint32_t IDESC_O = make_idesc_tf32(TILE, HEAD_DIM, false, true);
                 const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
                 auto issue_qk = [&](int t, int s) {
 #pragma unroll
                     for (int kk = 0; kk < HEAD_DIM / 8; ++kk)
-                        umma_ss_tf32(tmem + COL_S0 + t * TILE, kmajor_desc(q_addr + t * TILE_BYTES, kk, BOX_BYTES),
+                        umma_ss_tf32_lead(leader, tmem + COL_S0 + t * TILE, kmajor_desc(q_addr + t * TILE_BYTES, kk, BOX_BYTES),
                                      kmajor_desc(k_addr + s * TILE_BYTES, kk, BOX_BYTES), IDESC_S, kk > 0);
-                    umma_commit(&sh.s_full[t]);
+                    umma_commit_lead(leader, &sh.s_full[t]);
                 };
                 auto issue_pv = [&](int t, int s, bool first) {
 #pragma unroll
                     for (int kk = 0; kk < TILE / 8; ++kk)
-                        umma_ts_tf32(tmem + COL_O0 + t * HEAD_DIM, tmem + COL_S0 + t * TILE + kk * 8,
+                        umma_ts_tf32_lead(leader, tmem + COL_O0 + t * HEAD_DIM, tmem + COL_S0 + t * TILE + kk * 8,
                                      mnmajor_desc(v_addr + s * TILE_BYTES, kk, BOX_BYTES), IDESC_O,
                                      (!first || kk > 0) ? 1u : 0u);
-                    umma_commit(&sh.o_full[t]);
+                    umma_commit_lead(leader, &sh.o_full[t]);
                 };
-                bool ok = mbar_wait(wc, &sh.q_full, 0, W_QFULL);
-                if (ok) ok = mbar_wait(wc, &sh.k_full[0], 0, W_KFULL, 0);
+                bool ok = wait(&sh.q_full, 0, W_QFULL, 0);
+                if (ok) ok = wait(&sh.k_full[0], 0, W_KFULL, 0);
                 if (ok) {
                     tc_fence_after_sync();
                     if (0 < n0) issue_qk(0, 0);
                     if (0 < n1) issue_qk(1, 0);
-                    umma_commit(&sh.k_empty[0]);
+                    umma_commit_lead(leader, &sh.k_empty[0]);
                 }
                 for (int j = 0; ok && j < n; ++j) {
                     const int s = j % NST, s1 = (j + 1) % NST;
                     const uint32_t par = (j / NST) & 1, par1 = ((j + 1) / NST) & 1;
-                    stamp(a, tl, j, 0, 0);
-                    if (!(ok = mbar_wait(wc, &sh.v_full[s], par, W_VFULL, j))) break;
+                    stamp(a, tlm, j, 0, 0);
+                    if (!(ok = wait(&sh.v_full[s], par, W_VFULL, j))) break;
                     bool k_next_ready = false;
                     for (int t = 0; t < 2; ++t) {
                         const int nt = t == 0 ? n0 : n1;
                         if (j < nt) {
-                            if (!(ok = mbar_wait(wc, &sh.p_full[t], j & 1, W_PFULL, j))) break;
-                            stamp(a, tl, j, 0, 1 + 3 * t);
+                            if (!(ok = wait(&sh.p_full[t], j & 1, W_PFULL, j))) break;
+                            stamp(a, tlm, j, 0, 1 + 3 * t);
                             tc_fence_after_sync();
                             issue_pv(t, s, j == 0);
-                            stamp(a, tl, j, 0, 2 + 3 * t);
+                            stamp(a, tlm, j, 0, 2 + 3 * t);
                         }
-                        if (t == 1) umma_commit(&sh.v_empty[s]);
+                        if (t == 1) umma_commit_lead(leader, &sh.v_empty[s]);
                         if (j + 1 < nt) {
                             if (!k_next_ready) {
-                                if (!(ok = mbar_wait(wc, &sh.k_full[s1], par1, W_KFULL, j + 1))) break;
+                                if (!(ok = wait(&sh.k_full[s1], par1, W_KFULL, j + 1))) break;
                                 tc_fence_after_sync();
                                 k_next_ready = true;
                             }
                             issue_qk(t, s1);
-                            stamp(a, tl, j, 0, 3 + 3 * t);
+                            stamp(a, tlm, j, 0, 3 + 3 * t);
                         }
                     }
                     if (!ok) break;
-                    if (j + 1 < n) umma_commit(&sh.k_empty[s1]);
+                    if (j + 1 < n) umma_commit_lead(leader, &sh.k_empty[s1]);
                 }
             }
         }

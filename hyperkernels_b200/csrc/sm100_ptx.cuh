@@ -260,6 +260,23 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
+// 16 lanes x 64 consecutive columns in the accumulator-fragment shape (16x256b, eight times): thread t of the warp
+// receives, for each group j of eight columns, r[4j], r[4j+1] = lane (t >> 2), columns 8j + 2(t & 3) + {0, 1} and
+// r[4j+2], r[4j+3] = lane (t >> 2) + 8, same columns -- four threads hold 32 consecutive bytes of a row, so that
+// what they write to global memory falls into whole sectors.  taddr names the first of the 16 lanes.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
 // Pointer flavours for slices of a larger register array (indices must be
 // compile-time constants after unrolling so the array stays in registers).
 __device__ __forceinline__ void tmem_ld32p(uint32_t taddr, uint32_t* r) {
@@ -349,6 +366,49 @@ __device__ __forceinline__ void umma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, u
         : "memory");
 }
 
+// Warp-wide flavours.  A tcgen05.mma is issued by ONE thread, but its 64-bit descriptors and
+// addresses are warp-uniform values: when the whole warp runs the issuing code and only the
+// instruction itself is predicated on the elected lane (`leader` = elect_one_sync(), nonzero in
+// one lane), the compiler keeps that arithmetic on the uniform datapath.  Issued from inside a
+// divergent `if (lane == 0)` region instead, every operand is moved lane-wise and one thread
+// sustains only one M128 N64 MMA per ~54 cycles (measured) instead of one per ~36.
+__device__ __forceinline__ void umma_ss_tf32_lead(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                  uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "setp.ne.b32 q, %5, 0;\n"
+        "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_ts_tf32_lead(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                  uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "setp.ne.b32 q, %5, 0;\n"
+        "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_lead(uint32_t leader, uint64_t* bar) {
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "setp.ne.b32 q, %1, 0;\n"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+        "}\n"
+        ::"r"(smem_u32(bar)), "r"(leader)
+        : "memory");
+}
+
 // mbarrier arrives once all tcgen05.mma issued so far by this thread have completed
 // (implies tcgen05.fence::before_thread_sync).
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -371,6 +431,11 @@ __device__ __forceinline__ uint32_t tf32_round_bits(uint32_t bits) { return (bit
 // Same value as seen by the tensor core, which drops the low 13 bits itself:
 // for operands written by a kernel straight into tensor or shared memory.
 __device__ __forceinline__ uint32_t tf32_round_bits_mma(uint32_t bits) { return bits + 0x1000u; }
+
+__device__ __forceinline__ void red_add_v2(float* gptr, uint32_t a, uint32_t b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(gptr), "f"(__uint_as_float(a)), "f"(__uint_as_float(b))
+                 : "memory");
+}
 
 __device__ __forceinline__ void red_add_v4(float* gptr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b), "f"(c), "f"(d)

@@ -167,15 +167,56 @@ def _every_head_against_reference_kernels(B, H, T, causal, sigma, stress, seed, 
     dQ2, dK2, dV2, _ = hk.attention_backward(Q, K, V, O2, dO, LSE2, SCALE, causal)
     torch.cuda.synchronize()
     assert hk.last_device_status() == 0
-    worst = {}
+    worst, bad = {}, {}
     for name, a, r in (("O", O2, O), ("dQ", dQ2, dQ), ("dK", dK2, dK), ("dV", dV2, dV)):
         ma, rl = _per_head_errors(a, r)
         worst[name] = (float(ma.max()), float(rl.max()))
         scale_abs = max(1.0, float(r.abs().max()) / 5.0)  # the absolute gate is stated for outputs of magnitude <= 5
-        assert float(rl.max()) <= rel_gate, (name, worst[name])
-        assert float(ma.max()) <= abs_gate * scale_abs, (name, worst[name])
-    assert float((LSE2 - LSE).abs().max()) <= (2e-2 if stress else 2e-3)
+        over = torch.nonzero((rl > rel_gate) | (ma > abs_gate * scale_abs)).tolist()
+        if over:
+            bad[name] = over
+    lse_gate = 2e-2 if stress else 2e-3
+    lse_err = (LSE2 - LSE).abs().amax(-1)  # per head
+    worst["LSE"] = float(lse_err.max())
+    if torch.nonzero(lse_err > lse_gate).numel():
+        bad["LSE"] = torch.nonzero(lse_err > lse_gate).tolist()
     print(f"every head of B{B} H{H} T{T} vs the reference kernels (worst max-abs, worst rel-L2):", worst)
+    if bad and T <= 4096:
+        # The two kernel sets disagree on some head: float64 attention of that head (autograd) says which one is off.
+        # The reference's sm_89 forward, recompiled for this GPU, is not always reproducible at the B32 H25 shape (a few
+        # heads of O come out 1e-2 off from run to run, and D, hence dQ, with them); a head where the reference is
+        # the one that deviates is reported and skipped, a head where OURS deviates fails the test.
+        heads = sorted({(bi, hi) for hs in bad.values() for (bi, hi) in hs})
+        assert len(heads) <= 16, ("too many disagreeing heads to arbitrate", worst)
+        report = []
+        for (bi, hi) in heads:
+            ex = _exact_head(Q, K, V, dO, bi, hi, causal)
+            for name, mine_t, theirs_t in (("O", O2, O), ("dQ", dQ2, dQ), ("dK", dK2, dK), ("dV", dV2, dV)):
+                mine, theirs = mine_t[bi, hi].double(), theirs_t[bi, hi].double()
+                e_mine = float((mine - ex[name]).norm() / ex[name].norm())
+                e_theirs = float((theirs - ex[name]).norm() / ex[name].norm())
+                report.append((name, bi, hi, e_mine, e_theirs))
+                assert e_mine <= 1e-3, ("ours deviates from float64", name, bi, hi, e_mine, e_theirs)
+            e_mine = float((LSE2[bi, hi].double() - ex["LSE"]).abs().max())
+            e_theirs = float((LSE[bi, hi].double() - ex["LSE"]).abs().max())
+            report.append(("LSE", bi, hi, e_mine, e_theirs))
+            assert e_mine <= 2e-3, ("ours deviates from float64", "LSE", bi, hi, e_mine, e_theirs)
+        print("heads where the reference kernels deviate (tensor, b, h, ours vs float64, reference vs float64):",
+              [r for r in report if r[4] > 1e-3])
+    else:
+        assert not bad, (bad, worst)
+
+
+def _exact_head(Q, K, V, dO, b, h, causal):
+    """float64 attention forward and backward of one (b, h) slice on the device (autograd)."""
+    q, k, v = (t[b, h].double().clone().requires_grad_(True) for t in (Q, K, V))
+    s = (q @ k.T) * SCALE
+    if causal:
+        n = s.shape[0]
+        s = s.masked_fill(torch.triu(torch.ones(n, n, device=s.device, dtype=torch.bool), 1), float("-inf"))
+    o = torch.softmax(s, -1) @ v
+    o.backward(dO[b, h].double())
+    return {"O": o.detach(), "dQ": q.grad, "dK": k.grad, "dV": v.grad, "LSE": torch.logsumexp(s.detach(), -1)}
 
 
 # Two TF32 kernels with different summation orders differ from each other by up to the sum of their own errors against
