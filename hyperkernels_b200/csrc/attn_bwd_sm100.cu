@@ -31,9 +31,11 @@
 // refuses the 32-byte-chunk swizzle for a K-major operand), so TMA brings each
 // of them into shared memory twice, once per swizzle.
 //
-// Tensor-pipe order per query tile i (one issuing warp):
-//     dV(i) | S^T(i+1) | dK(i) | dP^T(i+1)
-// with dQ(i) issued by a second warp as soon as dS(i) is staged.
+// Tensor-pipe order per query tile i:
+//     dV(i) | S^T(i+1) | dK(i) | dP^T(i+1) | dQ(i)
+// dV(i) starts as soon as P^T(i) is in tensor memory, i.e. before the compute
+// warps have formed dS(i); dK(i) follows when dS^T(i) is there, dQ(i) when dS(i)
+// is staged in shared memory.
 // S^T(i+1) only needs the P^T columns back, i.e. dV(i); issuing it before dK(i)
 // lets the compute warps start the exponentials of tile i+1 -- the longest
 // stretch of scalar work -- while dK(i), dP^T(i+1) and dQ(i) execute.  Two of the
@@ -49,10 +51,9 @@
 //               owning 32 of the 128 query columns, all held in registers so
 //               that S^T and dP^T are read from tensor memory exactly once
 //   warp 16     TMA loads (K, V once; Q and dO per query tile, each in two layouts)
-//   warp 17     MMA issuer of dV, S^T, dK, dP^T (the whole warp runs the issuing
-//               code, one elected lane issues)
-//   warp 18     MMA issuer of dQ
-//   warp 19     TMA reductions of dQ (per query tile) and stores of dK, dV (at the end)
+//   warp 17     MMA issuer (the whole warp runs the issuing code, one elected lane
+//               issues)
+//   warp 18     TMA reductions of dQ (per query tile) and stores of dK, dV (at the end)
 #include <mutex>
 
 #include "attn_kernels.cuh"
@@ -63,8 +64,8 @@ namespace hk {
 namespace bwd {
 
 constexpr int NUM_COMPUTE = 512;
-constexpr int NUM_THREADS = NUM_COMPUTE + 128;  // 16 compute warps, 4 control warps
-constexpr int W_LOAD = 16, W_MMA = 17, W_MMA_DQ = 18, W_STORE = 19;
+constexpr int NUM_THREADS = NUM_COMPUTE + 96;  // 16 compute warps, 3 control warps
+constexpr int W_LOAD = 16, W_MMA = 17, W_STORE = 18;
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0;     // S^T, then P^T
 constexpr int COL_DP = 128;  // dP^T, then dS^T
@@ -80,8 +81,10 @@ struct __align__(16) Shared {
     uint64_t v_ready;       // V is in tensor memory (and its landing buffer is free)
     uint64_t qk_free, dok_free;  // S^T(i) / dP^T(i) complete: the K-major Q / dO tile may be refilled
     uint64_t s_full, dp_full;
-    uint64_t pt_ready;      // P^T is in tensor memory: dV += P^T dO (and then the next tile's S^T) may go
-    uint64_t p_ready;       // dS^T is in tensor memory too: dK += dS^T Q (and then the next tile's dP^T) may go
+    // per column group (32 query columns = four K = 8 slices of dV and dK): the warps of a group arrive together, the
+    // groups one after the other (the schedulers favour the older warps), and each group's slices go as soon as it is in
+    uint64_t pt_ready[4];   // P^T of the group is in tensor memory: its slices of dV += P^T dO may go
+    uint64_t p_ready[4];    // dS^T of the group is in tensor memory: its slices of dK += dS^T Q may go
     uint64_t dv_done, dk_done;   // dV(i) / dK(i) complete: the MN-major dO / Q tile is free
     uint64_t ds_ready, dq_full, dq_empty, staged;
     uint64_t acc_staged;    // dV, dK of the CTA are staged for the bulk store
@@ -96,9 +99,9 @@ constexpr int OFF_KM = TILE_BYTES;       // K, MN-major swizzle  (dQ = dS K)
 constexpr int OFF_QK = 2 * TILE_BYTES;   // Q, K-major           (S^T); staging of the last dQ
 constexpr int OFF_DOK = 3 * TILE_BYTES;  // dO, K-major          (dP^T)
 constexpr int OFF_QM = 4 * TILE_BYTES;   // Q, MN-major          (dK += dS^T Q); dV staging at the end
-constexpr int OFF_DOM = 5 * TILE_BYTES;  // dO, MN-major         (dV += P^T dO); dS boxes 0, 1 ([128 kv][32 q] each) once dV is done
-constexpr int OFF_DS = 6 * TILE_BYTES;   // dS boxes 2, 3; before them the dQ tile on its way out; first of all the landing buffer of V
-static_assert(OFF_DS == OFF_DOM + 2 * BOX_BYTES, "the four dS boxes are one descriptor: equally spaced");
+constexpr int OFF_DS = 5 * TILE_BYTES;   // dS boxes 0, 1 ([128 kv][32 q] each); first of all the landing buffer of V
+constexpr int OFF_DOM = 6 * TILE_BYTES;  // dO, MN-major         (dV += P^T dO); dS boxes 2, 3 once dV is done
+static_assert(OFF_DOM == OFF_DS + 2 * BOX_BYTES, "the four dS boxes are one descriptor: equally spaced");
 constexpr int OFF_SH = 7 * TILE_BYTES;
 // no slack for re-aligning the dynamic shared-memory base: it is declared 1024-byte aligned
 // and the kernel checks that it is (the 128-byte swizzles need it)
@@ -152,7 +155,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     uint8_t* sdO = smem + OFF_DOK;
     uint8_t* sQm = smem + OFF_QM;
     uint8_t* sdOm = smem + OFF_DOM;
-    uint8_t* sdS = smem + OFF_DOM;  // box b at sdS + b * BOX_BYTES
+    uint8_t* sdS = smem + OFF_DS;  // box b at sdS + b * BOX_BYTES
     Shared& sh = *reinterpret_cast<Shared*>(smem + OFF_SH);
 
     const int warp = threadIdx.x >> 5;
@@ -187,14 +190,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         mbar_init(&sh.dok_free, 1);
         mbar_init(&sh.s_full, 1);
         mbar_init(&sh.dp_full, 1);
-        mbar_init(&sh.pt_ready, NUM_COMPUTE);
-        mbar_init(&sh.p_ready, NUM_COMPUTE);
+        for (int g = 0; g < 4; ++g) {
+            mbar_init(&sh.pt_ready[g], TILE);
+            mbar_init(&sh.p_ready[g], TILE);
+        }
         mbar_init(&sh.dv_done, 1);
         mbar_init(&sh.dk_done, 1);
         mbar_init(&sh.ds_ready, NUM_COMPUTE);
         mbar_init(&sh.dq_full, 1);
-        mbar_init(&sh.dq_empty, NUM_COMPUTE);
-        mbar_init(&sh.dq_staged, NUM_COMPUTE);
+        mbar_init(&sh.dq_empty, 256);   // column groups 2, 3 drain dQ
+        mbar_init(&sh.dq_staged, 256);
         mbar_init(&sh.dq_out, 1);
         mbar_init(&sh.staged, 256);    // the threads that stage LSE and D
         mbar_init(&sh.acc_staged, NUM_COMPUTE);
@@ -305,8 +310,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             const bool tlm = tl && leader;
             constexpr uint32_t IDESC_ST = make_idesc_tf32(TILE, TILE, false, false);     // K-major x K-major, N = 128
             constexpr uint32_t IDESC_TS = make_idesc_tf32(TILE, HEAD_DIM, false, true);  // tmem A, MN-major B, N = 64
+            constexpr uint32_t IDESC_DQ = make_idesc_tf32(TILE, HEAD_DIM, true, true);   // MN-major A and B, N = 64
             const uint32_t k_addr = smem_u32(sK), q_addr = smem_u32(sQ), do_addr = smem_u32(sdO), qm_addr = smem_u32(sQm),
-                           dom_addr = smem_u32(sdOm);
+                           dom_addr = smem_u32(sdOm), km_addr = smem_u32(sKm), ds_addr = smem_u32(sdS);
             // S^T of query tile `it` (local index) as soon as K and Q have landed; the exponentials need nothing else
             auto issue_st = [&](int it) -> bool {
                 if (it == 0 && !wait(&sh.k_full, 0, W_KVFULL, 0)) return false;
@@ -337,29 +343,51 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 const uint32_t par = it & 1;
                 stamp(a, tlm, it, 0, 0);
                 if (!(ok = wait(&sh.dom_full, par, W_QMFULL, it))) break;
-                if (!(ok = wait(&sh.pt_ready, par, W_PREADY, it))) break;
                 stamp(a, tlm, it, 0, 1);
-                tc_fence_after_sync();
+                for (int g = 0; ok && g < 4; ++g) {  // dV += P^T dO, group by group
+                    if (!(ok = wait(&sh.pt_ready[g], par, W_PREADY, 4 * it + g))) break;
+                    tc_fence_after_sync();
 #pragma unroll
-                for (int kk = 0; kk < TILE / 8; ++kk)  // dV += P^T dO
-                    umma_ts_tf32_lead(leader, tmem + COL_DV, tmem + COL_S + kk * 8, mnmajor_desc(dom_addr, kk, BOX_BYTES), IDESC_TS,
-                                 (it > 0 || kk > 0) ? 1u : 0u);
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const int kk = 4 * g + k4;
+                        umma_ts_tf32_lead(leader, tmem + COL_DV, tmem + COL_S + kk * 8, mnmajor_desc(dom_addr, kk, BOX_BYTES),
+                                          IDESC_TS, (it > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
+                if (!ok) break;
                 umma_commit_lead(leader, &sh.dv_done);  // MN-major dO consumed: two of the dS boxes may be staged over it
                 stamp(a, tlm, it, 0, 2);
                 // next tile's S^T: P^T of this tile was consumed by the MMAs just issued
                 if (it + 1 < n_it && !(ok = issue_st(it + 1))) break;
                 stamp(a, tlm, it, 0, 3);
                 if (!(ok = wait(&sh.qm_full, par, W_QMFULL, 1000 + it))) break;
-                if (!(ok = wait(&sh.p_ready, par, W_PREADY, 1000 + it))) break;
-                tc_fence_after_sync();
+                for (int g = 0; ok && g < 4; ++g) {  // dK += dS^T Q, group by group
+                    if (!(ok = wait(&sh.p_ready[g], par, W_PREADY, 1000 + 4 * it + g))) break;
+                    tc_fence_after_sync();
 #pragma unroll
-                for (int kk = 0; kk < TILE / 8; ++kk)  // dK += dS^T Q
-                    umma_ts_tf32_lead(leader, tmem + COL_DK, tmem + COL_DP + kk * 8, mnmajor_desc(qm_addr, kk, BOX_BYTES), IDESC_TS,
-                                 (it > 0 || kk > 0) ? 1u : 0u);
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const int kk = 4 * g + k4;
+                        umma_ts_tf32_lead(leader, tmem + COL_DK, tmem + COL_DP + kk * 8, mnmajor_desc(qm_addr, kk, BOX_BYTES),
+                                          IDESC_TS, (it > 0 || kk > 0) ? 1u : 0u);
+                    }
+                }
+                if (!ok) break;
                 umma_commit_lead(leader, &sh.dk_done);  // MN-major Q consumed
                 // next tile's dP^T: dS^T of this tile was consumed by the MMAs just issued
                 if (it + 1 < n_it && !(ok = issue_dp(it + 1))) break;
                 stamp(a, tlm, it, 0, 4);
+                // dQ = dS K once dS is staged (shortly after dS^T was stored) and the previous dQ has left tensor memory
+                if (!(ok = wait(&sh.ds_ready, par, W_DSREADY, it))) break;
+                if (it > 0 && !(ok = wait(&sh.dq_empty, (it - 1) & 1, W_DQEMPTY, it))) break;
+                if (it == 0 && !(ok = wait(&sh.km_full, 0, W_KVFULL, 2))) break;
+                stamp(a, tlm, it, 0, 5);
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < TILE / 8; ++kk)
+                    umma_ss_tf32_lead(leader, tmem + COL_DQ, mnmajor_desc(ds_addr, kk, BOX_BYTES),
+                                      mnmajor_desc(km_addr, kk, BOX_BYTES), IDESC_DQ, kk > 0);
+                umma_commit_lead(leader, &sh.dq_full);  // also: the dS staging area is free again
+                stamp(a, tlm, it, 0, 6);
                 stamp(a, tlm, it, 0, 7);
             }
         }
@@ -418,29 +446,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             // the copies have read their shared-memory sources; they complete on their own
             bulk_wait_group_read_all();
         }
-    } else if (warp == W_MMA_DQ) {
-        // ------------------------------ dQ issuer ------------------------------
-        // dQ(i) = dS(i) K goes as soon as dS(i) is staged, whatever the other issuing warp is doing: the tensor pipe
-        // takes instructions from both, and nothing orders dQ(i) against dK(i), S^T(i+1) or dP^T(i+1).
-        if (n_it > 0) {
-            const uint32_t leader = elect_one_sync();
-            auto wait = [&](uint64_t* bar, uint32_t parity, int id, int aux) -> bool {
-                return __all_sync(0xffffffffu, mbar_wait(wc, bar, parity, id, aux));
-            };
-            constexpr uint32_t IDESC_DQ = make_idesc_tf32(TILE, HEAD_DIM, true, true);   // MN-major A and B, N = 64
-            const uint32_t km_addr = smem_u32(sKm), ds_addr = smem_u32(sdS);
-            bool ok = wait(&sh.km_full, 0, W_KVFULL, 2);
-            for (int it = 0; ok && it < n_it; ++it) {
-                if (!(ok = wait(&sh.ds_ready, it & 1, W_DSREADY, it))) break;
-                if (it > 0 && !(ok = wait(&sh.dq_empty, (it - 1) & 1, W_DQEMPTY, it))) break;
-                tc_fence_after_sync();
-#pragma unroll
-                for (int kk = 0; kk < TILE / 8; ++kk)  // dQ = dS K
-                    umma_ss_tf32_lead(leader, tmem + COL_DQ, mnmajor_desc(ds_addr, kk, BOX_BYTES),
-                                      mnmajor_desc(km_addr, kk, BOX_BYTES), IDESC_DQ, kk > 0);
-                umma_commit_lead(leader, &sh.dq_full);  // also: the dS staging area is free again
-            }
-        }
     } else {
         // ------------------------------ compute ------------------------------
         const int quarter = warp & 3;
@@ -472,23 +477,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         };
         float staged_val = (tid < 2 * TILE && n_it > 0) ? fetch_lse_or_d(it0 * TILE) : 0.f;
 
-        // dQ of query tile j out of tensor memory into the K-major dO tile (this thread: query row `row`, columns
-        // 16*part..16*part+15), in the layout of a 128-byte-swizzled TMA box: 16-byte chunk c of row r at position
-        // c ^ (r & 7).  Called between the two halves of the NEXT tile's compute, when dP^T of that tile is done: its
-        // operand, the K-major dO tile, is then dead until the tile after it is prefetched, long enough for the bulk
-        // reduction, which keeps its source for ~1 600 cycles.
-        auto drain_dq = [&](int j) -> bool {
+        // dQ of query tile j out of tensor memory into the K-major dO tile (column groups 2 and 3 only: this thread's
+        // query row `row`, 32 columns), in the layout of a 128-byte-swizzled TMA box: 16-byte chunk c of row r at
+        // position c ^ (r & 7).  Called between the two halves of the NEXT tile's compute, when dP^T of that tile is
+        // done: its operand, the K-major dO tile, is then dead until the tile after it is prefetched, long enough for
+        // the bulk reduction, which keeps its source for ~1 600 cycles.  Groups 2, 3 run behind groups 0, 1 (the
+        // schedulers favour the older warps), late enough for dQ(j) to be complete when they get here.
+        auto drain_dq = [&](int j, uint32_t (&v)[32]) -> bool {
             if (!__all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, j & 1, W_DQFULL, j))) return false;
             tc_fence_after_sync();
-            uint32_t v[16];
-            tmem_ld16(trow + COL_DQ + 16 * part, v);
+            tmem_ld32(trow + COL_DQ + 32 * (part & 1), v);
             tmem_wait_ld();
             tc_fence_before_sync();
             mbar_arrive(&sh.dq_empty);  // dQ is in registers: the next dQ = dS K may overwrite tensor memory
-            uint8_t* srow = sdO + (part >> 1) * BOX_BYTES + row * 128;
+            uint8_t* srow = sdO + (part & 1) * BOX_BYTES + row * 128;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                *reinterpret_cast<uint4*>(srow + (((4 * (part & 1) + c) ^ (row & 7)) << 4)) =
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(srow + ((c ^ (row & 7)) << 4)) =
                     make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
             fence_proxy_async_smem();
             mbar_arrive(&sh.dq_staged);
@@ -635,14 +640,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tmem_st32(trow + COL_S + c0, rp);
                 tmem_wait_st();
                 tc_fence_before_sync();
-                mbar_arrive(&sh.pt_ready);
+                mbar_arrive(&sh.pt_ready[part]);
             }
             ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dp_full, it & 1, W_SFULL, 1000 + it));
             if (!ok) break;
             stamp(a, tlc, it, 1, 11);
             tc_fence_after_sync();
+            if (it > 0 && part >= 2 && !(ok = drain_dq(it - 1, rp))) break;  // rp is free until dP^T is loaded
             tmem_ld32(trow + COL_DP + c0, rp);
-            if (it > 0 && !(ok = drain_dq(it - 1))) break;  // while the load is in flight
             tmem_wait_ld();
             stamp(a, tlc, it, 1, 3);
 
@@ -678,17 +683,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tmem_wait_st();
             stamp(a, tlc, it, 1, 13);
             tc_fence_before_sync();
-            mbar_arrive(&sh.p_ready);  // dK += dS^T Q may go
+            mbar_arrive(&sh.p_ready[part]);  // this group's slices of dK += dS^T Q may go
             stamp(a, tlc, it, 1, 5);
 
             // dS into shared memory, the MN-major A operand of dQ = dS K: box `part` holds query columns
-            // 32*part..32*part+31, one 128-byte row per key row, 32-byte chunks XOR-swizzled with (row & 3).  Boxes 2, 3
-            // have a buffer of their own, free once dQ of the previous tile is done (before the first tile it held V,
-            // which every thread has left once v_ready completes); boxes 0, 1 go over the MN-major dO tile as soon as
-            // dV of this tile is done.
-            if (part >= 2) {
-                // dQ of the previous tile is done: every thread waited for it when it drained that tile
-                if (it == 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.v_ready, 0, W_VREADY, 1));
+            // 32*part..32*part+31, one 128-byte row per key row, 32-byte chunks XOR-swizzled with (row & 3).  Boxes 0, 1
+            // -- the groups that get here first -- have a buffer of their own, free once dQ of the previous tile is done
+            // (before the first tile the buffer held V, which every thread has left once v_ready completes); boxes 2, 3 go over the MN-major dO tile as soon as dV of
+            // this tile is done.
+            if (part < 2) {
+                ok = __all_sync(0xffffffffu, it == 0 ? mbar_wait(wc, &sh.v_ready, 0, W_VREADY, 1)
+                                                      : mbar_wait(wc, &sh.dq_full, (it - 1) & 1, W_DQFULL, 1000 + it));
             } else {
                 ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dv_done, it & 1, W_DVDONE, it));
             }
