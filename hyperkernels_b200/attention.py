@@ -38,6 +38,7 @@ FLAG_ACCUM_DQ = 1 << 3
 FLAG_D_PRECOMPUTED = 1 << 4
 FLAG_REUSE_FWD_ROUNDED = 1 << 5
 FLAG_DROPOUT_SCALED = 1 << 6  # inverted dropout (kept terms / (1 - p), normaliser over all keys)
+FLAG_CONTINUE_SOFTMAX_STATE = 1 << 7  # forward: O, LSE hold the result over earlier keys; fold this call's keys in
 
 _f32p = C.POINTER(C.c_float)
 
@@ -229,8 +230,8 @@ def _workspace(nbytes: int, like, workspace):
 
 def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float = 0.0, dropout_mask=None,
                       philox_seed: Optional[int] = None, philox_offset: int = 0, q_pos0: int = 0, k_pos0: int = 0,
-                      bh_pos0: int = 0, prerounded: bool = False, dropout_scaled: bool = False, workspace=None,
-                      out=None, lse=None, stream=None):
+                      bh_pos0: int = 0, prerounded: bool = False, dropout_scaled: bool = False, continue_state: bool = False,
+                      workspace=None, out=None, lse=None, stream=None):
     """O, LSE = fused attention forward of [B,H,Tq,64] Q against [B,H,Tk,64] K, V (fp32 CUDA tensors)."""
     import torch
 
@@ -256,6 +257,9 @@ def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float =
         flags |= FLAG_OPERANDS_PREROUNDED
     if dropout_scaled:
         flags |= FLAG_DROPOUT_SCALED
+    if continue_state:
+        assert out is not None and lse is not None, "continue_state folds new keys into the given out / lse"
+        flags |= FLAG_CONTINUE_SOFTMAX_STATE
     p.flags = flags
     ws = _workspace(fwd_workspace_bytes(p), Q, workspace)
     if ws is not None:

@@ -240,7 +240,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                             if (!(ok = wait(&sh.p_full[t], j & 1, W_PFULL, j))) break;
                             stamp(a, tlm, j, 0, 1 + 3 * t);
                             tc_fence_after_sync();
-                            issue_pv(t, s, j == 0);
+                            issue_pv(t, s, j == 0 && !a.continue_state);
                             stamp(a, tlm, j, 0, 2 + 3 * t);
                         }
                         if (t == 1) umma_commit_lead(leader, &sh.v_empty[s]);
@@ -293,6 +293,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         float l = 0.f;
         bool ok = true;
         uint32_t r[128];
+        if (a.continue_state && nt > 0) {
+            // The result over the keys seen so far is the starting state: reference LSE, normaliser 1 and the running
+            // output O itself (a row that has seen no key starts from nothing).  The output accumulator is written
+            // before this thread's first arrival on p_full, which the first P V of the tile waits for.
+            const float lse0 = row_ok ? a.LSE[(int64_t)b * a.lse_sB + (int64_t)h * a.lse_sH + qrow] : -INFINITY;
+            const bool have = lse0 > -INFINITY;
+            m = have ? lse0 * LOG2E : -INFINITY;
+            l = have ? 1.f : 0.f;
+            const float4* orow = reinterpret_cast<const float4*>(a.O + (int64_t)b * a.o_sB + (int64_t)h * a.o_sH +
+                                                                 (int64_t)(row_ok ? qrow : 0) * a.o_sM);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float4 v = have ? orow[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                r[4 * i] = __float_as_uint(v.x); r[4 * i + 1] = __float_as_uint(v.y);
+                r[4 * i + 2] = __float_as_uint(v.z); r[4 * i + 3] = __float_as_uint(v.w);
+            }
+            tmem_st32p(tO, r);
+            tmem_st32p(tO + 32, r + 32);
+            tmem_wait_st();
+        }
 
         for (int j = 0; j < nt; ++j) {
             stamp(a, tls, j, 1 + t, 0);
@@ -341,7 +361,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             const bool raise = (m == -INFINITY) ? (m_cand > -INFINITY) : (m_cand > m + RESCALE_THRESHOLD);
             const float m_new = raise ? m_cand : m;
             const float alpha = raise ? ((m == -INFINITY) ? 0.f : ex2_approx(m - m_cand)) : 1.f;
-            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+            if ((j > 0 || a.continue_state) && __any_sync(0xffffffffu, raise)) {
                 // rescale the running output (PV of the previous step has completed: the commit that
                 // released S for this step was issued after it)
 #pragma unroll 1
@@ -442,11 +462,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             }
             fence_proxy_async_smem();
         }
-        if (row_ok)
+        // a tile that saw no key of this call leaves a continued result untouched
+        const bool keep_old = a.continue_state && nt == 0;
+        if (row_ok && !keep_old)
             a.LSE[(int64_t)b * a.lse_sB + (int64_t)h * a.lse_sH + qrow] = (l > 0.f) ? (m + log2f(l)) * LN2 : -INFINITY;
         // the 128 threads of this query tile (every one gets here, whatever `ok` is), then one of them stores
         asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");
-        if (row == 0 && q0 + t * TILE < a.Tq) {
+        if (row == 0 && q0 + t * TILE < a.Tq && !keep_old) {
             tma_store_4d(&mapO, sQ + t * TILE_BYTES, 0, q0 + t * TILE, h, b);
             tma_store_4d(&mapO, sQ + t * TILE_BYTES + BOX_BYTES, HALF_D, q0 + t * TILE, h, b);
             bulk_commit_group();

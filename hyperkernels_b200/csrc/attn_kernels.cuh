@@ -17,6 +17,7 @@ struct FwdArgs {
     int causal;
     int dropout_mode;  // 0 none, 1 dense mask, 2 Philox
     int drop_scaled;   // 1: inverted dropout (normaliser over all visible keys, kept terms times keep_scale)
+    int continue_state;  // 1: O, LSE hold the result over earlier keys and are the starting state
     float keep_scale;  // 1/(1-p) when drop_scaled, else 1
     uint32_t drop_thr;
     uint32_t bh_pos0;  // added to the local (batch, head) index in the Philox counter

@@ -311,6 +311,8 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     a.dropout_mode = mode;
     a.keep_scale = keep_scale_of(p->dropout_p, mode, p->flags);
     a.drop_scaled = (mode != 0 && (p->flags & HK_FLAG_DROPOUT_SCALED)) ? 1 : 0;
+    a.continue_state = (p->flags & HK_FLAG_CONTINUE_SOFTMAX_STATE) ? 1 : 0;
+    if (a.continue_state && a.drop_scaled) return HK_ERR_UNSUPPORTED;
     a.drop_thr = hk_philox_threshold(p->dropout_p);
     a.seed = p->dropout_seed; a.offset = p->dropout_offset; a.bh_pos0 = p->bh_pos0;
     a.status = device_status_ptr();

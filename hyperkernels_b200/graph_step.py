@@ -26,7 +26,8 @@ class GraphedAttentionStep:
     """
 
     def __init__(self, Q, K, V, dO, scale: float, causal: bool, *, dropout_p: float = 0.0,
-                 philox_seed: Optional[int] = None, philox_offset: int = 0, dropout_scaled: bool = False):
+                 philox_seed: Optional[int] = None, philox_offset: int = 0, dropout_scaled: bool = False,
+                 bh_pos0: int = 0):
         import torch
 
         B, H, T, _ = Q.shape
@@ -45,7 +46,7 @@ class GraphedAttentionStep:
             if philox_seed is None:
                 raise ValueError("dropout in a captured step uses the Philox mask: give philox_seed")
             drop = dict(dropout_p=dropout_p, philox_seed=philox_seed, philox_offset=philox_offset,
-                        dropout_scaled=dropout_scaled)
+                        dropout_scaled=dropout_scaled, bh_pos0=bh_pos0)
 
         def step():
             att.attention_forward(Q, K, V, scale, causal, workspace=self._ws, out=self.O, lse=self.LSE, **drop)

@@ -7,10 +7,13 @@ of Q (and of O, LSE, dO, dQ) and the K/V slices travel round the ring with
 overlapped with the compute of the step.  The compute of a step is a plain call
 of the single-GPU kernels through the C ABI on a (query segment, key segment)
 pair, told where the two segments sit in the global sequence
-(``q_pos0``/``k_pos0``); partial forward results are merged with
-``hk_attn_merge_partial``; in the backward each rank computes its contribution to
-the gradient of the visiting K/V block and adds it to an accumulator that
-travels one step behind the block.
+(``q_pos0``/``k_pos0``).  In the forward the running result of a query segment is
+the starting state of the next call (``HK_FLAG_CONTINUE_SOFTMAX_STATE``), so no
+partial outputs and no merge kernel exist; in the backward each rank computes its
+contribution to the gradient of the visiting K/V block and adds it to an
+accumulator that travels one step behind the block.  Every buffer a step needs
+(two K/V message buffers, the gradient accumulators, the rounded shards) is
+allocated once per shape and reused.
 
 Layouts: ``contiguous`` (rank r owns positions [r*T/G, (r+1)*T/G)) or ``zigzag``
 (the sequence is cut in 2G chunks and rank r owns chunks r and 2G-1-r, which
@@ -54,22 +57,19 @@ class CudaBackend:
 
         self.att = att
 
-    def prepare(self, x):
+    def prepare(self, x, out=None):
         """TF32-round a shard once, so that the per-pair calls can skip their rounding pre-pass (a K/V block is
         rounded by its owner and travels rounded)."""
-        return self.att.round_tf32(x.contiguous())
+        return self.att.round_tf32(x.contiguous(), out=out)
 
-    def fwd(self, Q, K, V, scale, causal, q_pos0, k_pos0):
-        return self.att.attention_forward(Q, K, V, scale, causal, q_pos0=q_pos0, k_pos0=k_pos0, prerounded=True)
+    def fwd_into(self, Q, K, V, scale, causal, q_pos0, k_pos0, O, LSE):
+        """Folds the keys of this block into the running result (O, LSE) of the query segment, in place."""
+        self.att.attention_forward(Q, K, V, scale, causal, q_pos0=q_pos0, k_pos0=k_pos0, prerounded=True, out=O, lse=LSE,
+                                   continue_state=True)
 
-    def merge(self, O_acc, LSE_acc, O_part, LSE_part):
-        self.att.merge_partial(O_acc, LSE_acc, O_part, LSE_part)
-
-    def precompute_D(self, dO, O):
-        import ctypes as C
-
+    def precompute_D(self, dO, O, out=None):
         B, H, T, _ = dO.shape
-        D = torch.empty((B, H, T), dtype=torch.float32, device=dO.device)
+        D = out if out is not None else torch.empty((B, H, T), dtype=torch.float32, device=dO.device)
         p = self.att.MemEfficientBwdParams()
         p.dO, p.O, p.D = dO.data_ptr(), O.data_ptr(), D.data_ptr()
         p.B, p.nh, p.T, p.scale = B, H, T, 1.0
@@ -87,6 +87,10 @@ class CudaBackend:
                                     prerounded=True)
 
 
+class RingError(RuntimeError):
+    """A hop of the ring did not complete: a peer failed, never joined, or the exchange timed out."""
+
+
 class RingAttention:
     """Attention of a sequence of length T sharded over the ranks of `group`.
 
@@ -94,7 +98,13 @@ class RingAttention:
     ``segments_of(rank, G, T, layout)``.
     """
 
-    def __init__(self, T: int, scale: float, causal: bool, group=None, layout: str = "zigzag", backend=None):
+    def __init__(self, T: int, scale: float, causal: bool, group=None, layout: str = "zigzag", backend=None,
+                 timeout_s: float = None):
+        """timeout_s: if set, every hop is waited for on the HOST with this limit and a hop that does not complete
+        raises RingError (failure detection for a peer that died or never joined; it costs the overlap of the host
+        with the GPU).  If None, completion is ordered on the stream only and a lost peer surfaces through the
+        process group's own timeout (NCCL watchdog)."""
+        self.timeout_s = timeout_s
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -116,18 +126,34 @@ class RingAttention:
 
     def _start_exchange(self, send_buf, recv_buf):
         if self.comm_stream is None:
-            return self._exchange(send_buf, recv_buf), None
+            try:
+                return self._exchange(send_buf, recv_buf), None
+            except Exception as e:
+                raise RingError(f"rank {self.rank}: could not post the exchange: {e}") from e
         # the communication stream must see the data the compute stream produced
         self.comm_stream.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(self.comm_stream):
-            reqs = self._exchange(send_buf, recv_buf)
+        try:
+            with torch.cuda.stream(self.comm_stream):
+                reqs = self._exchange(send_buf, recv_buf)
+        except Exception as e:
+            raise RingError(f"rank {self.rank}: could not post the exchange: {e}") from e
         return reqs, self.comm_stream
 
-    @staticmethod
-    def _finish(handle):
+    def _finish(self, handle):
         reqs, stream = handle
-        for r in reqs:
-            r.wait()
+        try:
+            for r in reqs:
+                if self.timeout_s is not None:
+                    import datetime
+
+                    if not r.wait(datetime.timedelta(seconds=self.timeout_s)):
+                        raise RingError("hop did not complete")
+                else:
+                    r.wait()
+        except RingError:
+            raise
+        except Exception as e:  # the process group reports a dead peer or a timeout as RuntimeError
+            raise RingError(f"rank {self.rank}: exchange with ranks {self._peer(-1)} / {self._peer(+1)} failed: {e}") from e
         if stream is not None:
             torch.cuda.current_stream().wait_stream(stream)
 
@@ -139,77 +165,102 @@ class RingAttention:
             off += n
         return out
 
+    def _buffers(self, like, n_kv=2):
+        """Preallocated per shard shape: rounded shards, two K/V message buffers, two gradient accumulators."""
+        key = (tuple(like.shape), like.device)
+        if getattr(self, "_buf_key", None) != key:
+            mk = lambda *lead: torch.empty(tuple(lead) + tuple(like.shape), dtype=torch.float32, device=like.device)
+            self._buf = dict(q=mk(), do=mk(), kv=[mk(2), mk(2)], acc=[mk(2), mk(2)], acc_in=mk(2), dq=mk(),
+                             d=torch.empty(like.shape[:3], dtype=torch.float32, device=like.device))
+            self._buf_key = key
+        return self._buf
+
     # ---- forward ------------------------------------------------------------------
     def forward(self, Q, K, V):
+        """O, LSE of this rank's query shard over the whole key sequence.  The returned tensors are fresh; everything
+        else is reused from call to call."""
         G = self.world
-        Q, K, V = self.backend.prepare(Q), self.backend.prepare(K), self.backend.prepare(V)
-        q_views = self._seg_views(Q, self.my_segs)
-        O_acc = [torch.zeros(v.shape, dtype=torch.float32, device=Q.device) for v in q_views]
-        LSE_acc = [torch.full(v.shape[:3], float("-inf"), dtype=torch.float32, device=Q.device) for v in q_views]
-        kv = torch.stack([K, V]).contiguous()  # one message per hop
+        buf = self._buffers(Q)
+        Qr = self.backend.prepare(Q, out=buf["q"])
+        kv = buf["kv"][0]
+        self.backend.prepare(K, out=kv[0])
+        self.backend.prepare(V, out=kv[1])
+        O = torch.empty_like(Q)
+        LSE = torch.full(Q.shape[:3], float("-inf"), dtype=torch.float32, device=Q.device)
+        q_views = self._seg_views(Qr, self.my_segs)
+        o_views = self._seg_views(O, self.my_segs)
+        l_views = self._seg_views(LSE, self.my_segs)
         for t in range(G):
             src = (self.rank - t) % G
+            src_segs = segments_of(src, G, self.T, self.layout)
             handle = None
             if t + 1 < G:
-                nxt = torch.empty_like(kv)
+                nxt = buf["kv"][(t + 1) & 1]
                 handle = self._start_exchange(kv, nxt)  # overlaps with the compute below
-            k_views = self._seg_views(kv[0], segments_of(src, G, self.T, self.layout))
-            v_views = self._seg_views(kv[1], segments_of(src, G, self.T, self.layout))
+            k_views = self._seg_views(kv[0], src_segs)
+            v_views = self._seg_views(kv[1], src_segs)
             for qi, qseg in enumerate(self.my_segs):
-                for ki, kseg in enumerate(segments_of(src, G, self.T, self.layout)):
-                    if not visible(qseg, kseg, self.causal):
-                        continue
-                    O_p, L_p = self.backend.fwd(q_views[qi], k_views[ki], v_views[ki], self.scale, self.causal,
-                                                qseg[0], kseg[0])
-                    self.backend.merge(O_acc[qi], LSE_acc[qi], O_p.contiguous(), L_p.contiguous())
+                for ki, kseg in enumerate(src_segs):
+                    if visible(qseg, kseg, self.causal):
+                        self.backend.fwd_into(q_views[qi], k_views[ki], v_views[ki], self.scale, self.causal, qseg[0],
+                                              kseg[0], o_views[qi], l_views[qi])
             if handle is not None:
                 self._finish(handle)
                 kv = nxt
-        return torch.cat(O_acc, dim=2), torch.cat(LSE_acc, dim=2)
+        if O.is_cuda:
+            # rows that saw no key at all keep the state they started from: O undefined, LSE = -inf
+            O.masked_fill_(torch.isinf(LSE).unsqueeze(-1), 0.0)
+        return O, LSE
 
     # ---- backward -----------------------------------------------------------------
     def backward(self, Q, K, V, O, LSE, dO):
         G = self.world
-        D = self.backend.precompute_D(dO.contiguous(), O.contiguous())
-        Q, K, V, dO = (self.backend.prepare(x) for x in (Q, K, V, dO))
-        q_views = self._seg_views(Q, self.my_segs)
-        do_views = self._seg_views(dO, self.my_segs)
+        buf = self._buffers(Q)
+        D = self.backend.precompute_D(dO.contiguous(), O.contiguous(), out=buf["d"])
+        Qr = self.backend.prepare(Q, out=buf["q"])
+        dOr = self.backend.prepare(dO, out=buf["do"])
+        kv = buf["kv"][0]
+        self.backend.prepare(K, out=kv[0])
+        self.backend.prepare(V, out=kv[1])
+        q_views = self._seg_views(Qr, self.my_segs)
+        do_views = self._seg_views(dOr, self.my_segs)
         o_views = self._seg_views(O, self.my_segs)
-        lse_views = [v.contiguous() for v in self._seg_views(LSE, self.my_segs)]
-        d_views = [v.contiguous() for v in self._seg_views(D, self.my_segs)]
+        lse_views = self._seg_views(LSE, self.my_segs)
+        d_views = self._seg_views(D, self.my_segs)
         dQ = torch.zeros_like(Q)
         dq_views = self._seg_views(dQ, self.my_segs)
-        kv = torch.stack([K, V]).contiguous()
-        acc = None  # gradient accumulator of the block processed in the previous step, on its way to the next rank
+        acc_in = buf["acc_in"]
         acc_handle = None
         for t in range(G):
             src = (self.rank - t) % G
             src_segs = segments_of(src, G, self.T, self.layout)
             kv_handle = None
             if t + 1 < G:
-                nxt = torch.empty_like(kv)
+                nxt = buf["kv"][(t + 1) & 1]
                 kv_handle = self._start_exchange(kv, nxt)
             k_views = self._seg_views(kv[0], src_segs)
             v_views = self._seg_views(kv[1], src_segs)
-            part = torch.zeros_like(kv)  # this rank's (dK, dV) contribution to the visiting block
+            # this rank's (dK, dV) contribution to the visiting block, on top of what the block has collected so
+            # far: the accumulator that left the previous rank one step ago
+            part = buf["acc"][t & 1]
+            if t > 0:
+                self._finish(acc_handle)
+                part.copy_(acc_in)
+            else:
+                part.zero_()
             pk_views = self._seg_views(part[0], src_segs)
             pv_views = self._seg_views(part[1], src_segs)
             for qi, qseg in enumerate(self.my_segs):
                 for ki, kseg in enumerate(src_segs):
-                    if not visible(qseg, kseg, self.causal):
-                        continue
-                    self.backend.bwd(q_views[qi], k_views[ki], v_views[ki], o_views[qi], do_views[qi], lse_views[qi],
-                                     d_views[qi], self.scale, self.causal, qseg[0], kseg[0], dq_views[qi], pk_views[ki],
-                                     pv_views[ki])
-            # the accumulator of this block left the previous rank one step ago
-            if t > 0:
-                self._finish(acc_handle)
-                part.add_(acc_in)
+                    if visible(qseg, kseg, self.causal):
+                        self.backend.bwd(q_views[qi], k_views[ki], v_views[ki], o_views[qi], do_views[qi], lse_views[qi],
+                                         d_views[qi], self.scale, self.causal, qseg[0], kseg[0], dq_views[qi],
+                                         pk_views[ki], pv_views[ki])
             if kv_handle is not None:
                 self._finish(kv_handle)
                 kv = nxt
-            acc = part
-            acc_in = torch.empty_like(acc)
-            acc_handle = self._start_exchange(acc, acc_in)  # t < G-1: to the next worker; t = G-1: the hop home
+            if G == 1:
+                return dQ, part[0].clone(), part[1].clone()
+            acc_handle = self._start_exchange(part, acc_in)  # t < G-1: to the next worker; t = G-1: the hop home
         self._finish(acc_handle)
-        return dQ, acc_in[0], acc_in[1]
+        return dQ, acc_in[0].clone(), acc_in[1].clone()

@@ -82,7 +82,13 @@ enum {
      * probabilities are multiplied by 1/(1-p) and the dropped ones are zero in O; LSE does not
      * depend on the mask.  p is dropout_p for a dense mask and floor(dropout_p * 65536) / 65536
      * for the Philox mask.  Without active dropout the flag changes nothing. */
-    HK_FLAG_DROPOUT_SCALED = 1u << 6
+    HK_FLAG_DROPOUT_SCALED = 1u << 6,
+    /* forward: O and LSE already hold the attention result over the keys seen so far (LSE = -inf, any O, for a
+     * row that has seen none); the call folds the keys of THIS call in and leaves the combined result in O and
+     * LSE -- the previous result acts as one more "key" of weight exp(LSE) and value O.  A caller that shards the
+     * key sequence (a KV ring) chains its calls this way instead of merging partial results afterwards.  Not
+     * available together with HK_FLAG_DROPOUT_SCALED.  No counterpart in the reference. */
+    HK_FLAG_CONTINUE_SOFTMAX_STATE = 1u << 7
 };
 
 /* ---- forward ------------------------------------------------------------

@@ -574,6 +574,29 @@ def test_merge_partial_equals_full():
     lse_check(host(LSE), L_ref)
 
 
+@pytest.mark.parametrize("causal", [0, 1])
+def test_chained_forward_over_key_blocks_equals_full(causal):
+    """HK_FLAG_CONTINUE_SOFTMAX_STATE: keys split into three blocks, attended one after the other into the same O and
+    LSE (the previous result is the starting state): equals attention over all keys; the order of the blocks does not
+    matter, and a block no query can see (causal, q_pos0 < k_pos0) leaves the result untouched."""
+    B, H, Tq, Tk = 2, 3, 300, 640
+    q_pos0 = 200 if causal else 0
+    Q, K, V = normal((B, H, Tq, 64), 83), normal((B, H, Tk, 64), 84), normal((B, H, Tk, 64), 85)
+    O_ref, L_ref = ol.attn_forward_mt(Q, K, V, SCALE, causal, q_pos0=q_pos0)
+    tQ, tK, tV = dev(Q), dev(K), dev(V)
+    cuts = [(0, 256), (256, 512), (512, 640)]
+    for order in ([0, 1, 2], [2, 0, 1]):
+        O = torch.full((B, H, Tq, 64), float("nan"), device="cuda")
+        LSE = torch.full((B, H, Tq), float("-inf"), device="cuda")
+        for bi in order:
+            k0, k1 = cuts[bi]
+            hk.attention_forward(tQ, tK[:, :, k0:k1].contiguous(), tV[:, :, k0:k1].contiguous(), SCALE, bool(causal),
+                                 q_pos0=q_pos0, k_pos0=k0, out=O, lse=LSE, continue_state=True)
+        ok_status()
+        gate("O", host(O), O_ref)
+        lse_check(host(LSE), L_ref)
+
+
 # ---------------------------------------------------------------------------
 # size-independent properties at full BASELINE sizes
 # ---------------------------------------------------------------------------

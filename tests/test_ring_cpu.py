@@ -1,7 +1,7 @@
 """CPU test of the sequence-sharded ring schedule (hyperkernels_b200/ring.py) on two gloo ranks.
 
-The schedule (who computes which (query segment, key segment) pair at which step, the merge of partial
-results, the travelling gradient accumulators, the message order) is host logic and is what is tested here;
+The schedule (who computes which (query segment, key segment) pair at which step, the chaining of
+the running forward result through the key blocks, the travelling gradient accumulators, the message order) is host logic and is what is tested here;
 the per-pair compute is done by a stand-in backend built on the CPU oracle, which exists only in this test.
 The same schedule with the CUDA backend is checked on GPUs in tests/test_ring_gpu.py.
 """
@@ -31,14 +31,17 @@ class OracleBackend:
     def _np(t):
         return np.ascontiguousarray(t.detach().cpu().numpy(), dtype=np.float32)
 
-    def prepare(self, x):
-        return x.contiguous()
+    def prepare(self, x, out=None):
+        if out is None:
+            return x.contiguous()
+        out.copy_(x)
+        return out
 
-    def fwd(self, Q, K, V, scale, causal, q_pos0, k_pos0):
+    def fwd_into(self, Q, K, V, scale, causal, q_pos0, k_pos0, O_acc, LSE_acc):
+        """Attention over this key block, folded into the running (O_acc, LSE_acc): what the CUDA forward does with
+        HK_FLAG_CONTINUE_SOFTMAX_STATE, restated with the oracle and a float64 merge."""
         O, L = self.ol.attn_forward(self._np(Q), self._np(K), self._np(V), scale, int(causal), None, q_pos0, k_pos0)
-        return torch.from_numpy(O), torch.from_numpy(L)
-
-    def merge(self, O_acc, LSE_acc, O_part, LSE_part):
+        O_part, LSE_part = torch.from_numpy(O), torch.from_numpy(L)
         la, lp = LSE_acc.double(), LSE_part.double()
         mx = torch.maximum(la, lp)
         safe = torch.where(torch.isinf(mx), torch.zeros_like(mx), mx)
@@ -46,11 +49,16 @@ class OracleBackend:
         tot = ea + ep
         wa = torch.where(tot > 0, ea / tot, torch.zeros_like(tot))
         wp = torch.where(tot > 0, ep / tot, torch.zeros_like(tot))
-        O_acc.copy_((O_acc.double() * wa[..., None] + O_part.double() * wp[..., None]).float())
+        o_old = torch.where(torch.isinf(la).unsqueeze(-1), torch.zeros_like(O_part, dtype=torch.float64), O_acc.double())
+        O_acc.copy_((o_old * wa[..., None] + O_part.double() * wp[..., None]).float())
         LSE_acc.copy_(torch.where(tot > 0, safe + torch.log(tot), torch.full_like(tot, float("-inf"))).float())
 
-    def precompute_D(self, dO, O):
-        return torch.from_numpy(self.ol.precompute_D(self._np(dO), self._np(O)))
+    def precompute_D(self, dO, O, out=None):
+        D = torch.from_numpy(self.ol.precompute_D(self._np(dO), self._np(O)))
+        if out is not None:
+            out.copy_(D)
+            return out
+        return D
 
     def bwd(self, Q, K, V, O, dO, LSE, D, scale, causal, q_pos0, k_pos0, dQ, dK, dV):
         _, dq, dk, dv = self.ol.attn_backward(self._np(Q), self._np(K), self._np(V), self._np(O), self._np(dO),
@@ -120,6 +128,59 @@ def test_ring_schedule_two_gloo_ranks(layout, causal):
         assert p.exitcode == 0
     # the oracle is fp32/fp64 throughout: only summation order differs from the one-piece computation
     assert max(errs) < 2e-5, errs
+
+
+def test_ring_of_one_rank_needs_no_exchange():
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    p = ctx.Process(target=_worker, args=(0, 1, 29877, "zigzag", True, 64, ret))
+    p.start()
+    errs = ret.get(timeout=120)
+    p.join(timeout=60)
+    assert p.exitcode == 0 and max(errs) < 2e-5, errs
+
+
+def _failing_worker(rank, world, port, ret):
+    """Rank 1 leaves before the first hop (a peer that died between steps); rank 0 must get a RingError from its
+    host-timed wait instead of hanging."""
+    import datetime
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    from hyperkernels_b200.ring import RingAttention, RingError
+
+    def leave():  # no clean shutdown of the process group: the process is simply gone
+        ret.close()
+        ret.join_thread()
+        os._exit(0)
+
+    if rank == 1:
+        ret.put(("left", 1))
+        leave()
+    x = torch.zeros((1, 1, 32, 64))
+    ring = RingAttention(64, 0.125, True, layout="zigzag", backend=OracleBackend(), timeout_s=3.0)
+    t0 = time.time()
+    try:
+        ring.forward(x, x, x)
+        ret.put(("no error", time.time() - t0))
+    except RingError:
+        ret.put(("RingError", time.time() - t0))
+    leave()
+
+
+def test_lost_peer_raises_ring_error_within_the_timeout():
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, 29911, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict([ret.get(timeout=60), ret.get(timeout=60)])
+    for p in procs:
+        p.join(timeout=30)
+    assert "RingError" in got, got
+    assert got["RingError"] < 15.0, got
 
 
 def test_segments_cover_sequence_once():
