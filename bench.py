@@ -335,7 +335,7 @@ def run_ours(args, cfg, rank, local_rank, world):
     # all samples (the mean is reported beside it).
     gstep = prob.capture()
     est = _median(timed_samples(gstep.replay, 5, flush, stream, torch))
-    inner = max(1, min(200, int(math.ceil(0.2 / max(args.steps * est * 1e-3, 1e-9)))))
+    inner = args.inner if args.inner > 0 else max(1, min(200, int(math.ceil(0.2 / max(args.steps * est * 1e-3, 1e-9)))))
     barrier()
     clocks = ClockSampler(local_rank)
     clocks.start()  # sampled from here to the end of the end-to-end loop
@@ -706,6 +706,8 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--inner", type=int, default=0,
+                    help="graph replays per driver step (0: as many as make the timed region ~0.2 s); 1 for profiler runs")
     ap.add_argument("--no-multi-gpu-configs", action="store_true",
                     help="N > 1: skip the strong_cfg4 and ring_cfg5 sub-records")
     ap.add_argument("--ring", type=int, default=2, help="config 5 on N > 1 GPUs: ranks per sequence ring")
