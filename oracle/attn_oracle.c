@@ -17,9 +17,11 @@
  * Parity status: the p=0 paths are pinned bit-for-bit against the reference's
  * own host functions compiled from its sources (see oracle/Makefile, target
  * _ref) and against the committed golden vectors.  The dropout path has no
- * counterpart in the reference's tests ("parity unpinned" for dropout): it is
- * pinned only by a finite-difference check and by the reference GPU kernel fed
- * the same dense mask.
+ * counterpart in the reference's host code or tests.  Its forward is pinned to
+ * the reference's GPU forward kernel (recompiled, fed the same dense mask) by
+ * tests/test_reference_kernels_gpu.py::test_dropout_forward_pinned_to_the_reference_kernel;
+ * its backward has no reference implementation at all ("parity unpinned") and
+ * is held by a float64 autograd check and finite differences.
  *
  * Tensors are contiguous [B,H,T,Hd] (LSE, D: [B,H,T]).  Tq query rows attend
  * to Tk key rows; query row i sits at global position q_pos0+i and key row j at
