@@ -15,18 +15,25 @@
 //                 two-stage ring (128-byte-swizzled boxes of 128 rows x 32
 //                 floats, mbarrier tx; V with the 32-byte-chunk swizzle an
 //                 MN-major TF32 operand needs).
-//   warp 1        MMA issuer (the whole warp runs the issuing code, one elected lane issues), in the order PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1):
+//   warp 1        MMA issuer (the whole warp runs the issuing code, one elected lane issues).
 //                 S_t = Q_t K^T is 8 tcgen05.mma (M128 N128 K8, operands from
 //                 shared memory), O_t += P_t V is 16 (M128 N64 K8, A = P_t read
-//                 from tensor memory, B = V MN-major from shared memory).
+//                 from tensor memory, B = V MN-major from shared memory).  The
+//                 (step, tile) products are numbered in the order (0,0) (0,1) (1,0)
+//                 (1,1) ...; product q keeps its S, then its P, in score buffer
+//                 q mod 3, and the issue order is S(0) S(1) S(2) | P V(0) S(3) |
+//                 P V(1) S(4) | ...: the scores of a tile's NEXT step are computed
+//                 while its softmax works on the current one (the tensor pipe
+//                 executes in issue order, so S(q+3) cannot overtake the P V(q)
+//                 that reads the same buffer).
 //   warps 4-7     softmax of tile 0, warps 8-11 softmax of tile 1: thread r owns
 //                 query row r (tensor-memory lane r), holds the 128 scores of a
 //                 step in registers (one tensor-memory read per score), writes P
 //                 back over S.  The running output is rescaled only when the
 //                 running maximum grew by more than 2^8 (the final O/l and LSE
 //                 use the same maximum, so the result is the same function).
-// Tensor memory: S_0, S_1 (128 columns each), O_0, O_1 (64 columns each).
-// Warps 0-3 give most of their registers to the softmax warps (setmaxnreg).
+// Tensor memory: three score buffers (128 columns each), O_0, O_1 (64 columns each): 512 of 512 columns.
+// Warps 0-3 give most of their registers to the softmax warps (setmaxnreg 56 / 224).
 #include <mutex>
 
 #include "attn_kernels.cuh"
@@ -38,13 +45,14 @@ namespace fwd {
 
 constexpr int NUM_THREADS = 384;
 constexpr int TMEM_COLS = 512;
-constexpr int COL_S0 = 0;    // S_t at COL_S0 + 128 t
 constexpr int COL_O0 = 256;  // O_t at COL_O0 + 64 t
+// score buffer b of three: columns 0, 128, 384
+__device__ __forceinline__ uint32_t score_col(int b) { return b == 2 ? 384u : (uint32_t)b * 128u; }
 constexpr int NST = 2;       // K/V ring depth
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 struct __align__(8) Shared {
-    uint64_t q_full, k_full[NST], k_empty[NST], v_full[NST], v_empty[NST], s_full[2], p_full[2], o_full[2];
+    uint64_t q_full, k_full[NST], k_empty[NST], v_full[NST], v_empty[NST], s_full[3], p_full[3], o_full[3];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -68,8 +76,10 @@ __device__ __forceinline__ void stamp(const FwdArgs& a, bool on, int j, int role
 __device__ __forceinline__ void stamp(const FwdArgs&, bool, int, int, int) {}
 #endif
 
-// 384 threads x 168 registers at launch = 128 x 48 + 256 x 224 after the hand-over
-__device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 48;\n"); }
+// 384 threads x 168 registers at launch = 128 x 56 + 256 x 224 after the hand-over (setmaxnreg.inc can only take what
+// the launch-time pool of the CTA holds)
+static_assert(128 * 56 + 256 * 224 <= NUM_THREADS * 168, "register hand-over exceeds the CTA's pool");
+__device__ __forceinline__ void reg_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n"); }
 __device__ __forceinline__ void reg_acquire() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;\n"); }
 
 // number of key tiles the 128-row query tile starting at local row q0 attends to
@@ -131,10 +141,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             mbar_init(&sh.v_full[s], 1);
             mbar_init(&sh.v_empty[s], 1);
         }
-        for (int t = 0; t < 2; ++t) {
-            mbar_init(&sh.s_full[t], 1);
-            mbar_init(&sh.p_full[t], 128);
-            mbar_init(&sh.o_full[t], 1);
+        // The score barriers belong to the score BUFFER, not to the tile: the warps of a tile may be a whole step
+        // apart (the scores of the next step are there before the slowest warp has finished this one), and a
+        // buffer is only refilled after every thread has handed over the P it held.
+        for (int bf = 0; bf < 3; ++bf) {
+            mbar_init(&sh.s_full[bf], 1);
+            mbar_init(&sh.p_full[bf], 128);
+            mbar_init(&sh.o_full[bf], 1);
         }
         sh.abort_flag = 0;
         fence_mbar_init();
@@ -205,57 +218,64 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 constexpr uint32_t IDESC_S = make_idesc_tf32(TILE, TILE, false, false);
                 constexpr uint32_t IDESC_O = make_idesc_tf32(TILE, HEAD_DIM, false, true);
                 const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-                auto issue_qk = [&](int t, int s) {
+                auto issue_qk = [&](int t, int s, int buf) {
+                    const uint32_t d = tmem + score_col(buf);
 #pragma unroll
                     for (int kk = 0; kk < HEAD_DIM / 8; ++kk)
-                        umma_ss_tf32_lead(leader, tmem + COL_S0 + t * TILE, kmajor_desc(q_addr + t * TILE_BYTES, kk, BOX_BYTES),
+                        umma_ss_tf32_lead(leader, d, kmajor_desc(q_addr + t * TILE_BYTES, kk, BOX_BYTES),
                                      kmajor_desc(k_addr + s * TILE_BYTES, kk, BOX_BYTES), IDESC_S, kk > 0);
-                    umma_commit_lead(leader, &sh.s_full[t]);
+                    umma_commit_lead(leader, &sh.s_full[buf]);
                 };
-                auto issue_pv = [&](int t, int s, bool first) {
+                auto issue_pv = [&](int t, int s, int buf, bool first) {  // O_t += P V, P in score buffer buf
+                    const uint32_t p = tmem + score_col(buf);
 #pragma unroll
                     for (int kk = 0; kk < TILE / 8; ++kk)
-                        umma_ts_tf32_lead(leader, tmem + COL_O0 + t * HEAD_DIM, tmem + COL_S0 + t * TILE + kk * 8,
+                        umma_ts_tf32_lead(leader, tmem + COL_O0 + t * HEAD_DIM, p + kk * 8,
                                      mnmajor_desc(v_addr + s * TILE_BYTES, kk, BOX_BYTES), IDESC_O,
                                      (!first || kk > 0) ? 1u : 0u);
-                    umma_commit_lead(leader, &sh.o_full[t]);
+                    umma_commit_lead(leader, &sh.o_full[buf]);
+                };
+                // products in issue order: step by step, tile 0 before tile 1 (a tile takes part while j < n_t)
+                const int total = n0 + n1;
+                auto advance = [&](int& j, int& t) {
+                    if (t == 0 && j < n1) {
+                        t = 1;
+                    } else {
+                        ++j;
+                        t = (j < n0) ? 0 : 1;
+                    }
+                };
+                int jq = 0, tq = (n0 > 0) ? 0 : 1, nq = 0;  // the next S = Q K^T to issue and its number
+                auto next_qk = [&]() -> bool {
+                    if (nq >= total) return true;
+                    const int s = jq % NST;
+                    if (tq == 0 || jq >= n0) {  // first product that reads this key tile
+                        if (!wait(&sh.k_full[s], (jq / NST) & 1, W_KFULL, jq)) return false;
+                        tc_fence_after_sync();
+                    }
+                    issue_qk(tq, s, nq % 3);
+                    if (tq == 1 || jq >= n1) umma_commit_lead(leader, &sh.k_empty[s]);  // last one that reads it
+                    ++nq;
+                    advance(jq, tq);
+                    return true;
                 };
                 bool ok = wait(&sh.q_full, 0, W_QFULL, 0);
-                if (ok) ok = wait(&sh.k_full[0], 0, W_KFULL, 0);
-                if (ok) {
-                    tc_fence_after_sync();
-                    if (0 < n0) issue_qk(0, 0);
-                    if (0 < n1) issue_qk(1, 0);
-                    umma_commit_lead(leader, &sh.k_empty[0]);
-                }
-                for (int j = 0; ok && j < n; ++j) {
-                    const int s = j % NST, s1 = (j + 1) % NST;
-                    const uint32_t par = (j / NST) & 1, par1 = ((j + 1) / NST) & 1;
-                    stamp(a, tlm, j, 0, 0);
-                    if (!(ok = wait(&sh.v_full[s], par, W_VFULL, j))) break;
-                    bool k_next_ready = false;
-                    for (int t = 0; t < 2; ++t) {
-                        const int nt = t == 0 ? n0 : n1;
-                        if (j < nt) {
-                            if (!(ok = wait(&sh.p_full[t], j & 1, W_PFULL, j))) break;
-                            stamp(a, tlm, j, 0, 1 + 3 * t);
-                            tc_fence_after_sync();
-                            issue_pv(t, s, j == 0 && !a.continue_state);
-                            stamp(a, tlm, j, 0, 2 + 3 * t);
-                        }
-                        if (t == 1) umma_commit_lead(leader, &sh.v_empty[s]);
-                        if (j + 1 < nt) {
-                            if (!k_next_ready) {
-                                if (!(ok = wait(&sh.k_full[s1], par1, W_KFULL, j + 1))) break;
-                                tc_fence_after_sync();
-                                k_next_ready = true;
-                            }
-                            issue_qk(t, s1);
-                            stamp(a, tlm, j, 0, 3 + 3 * t);
-                        }
+                for (int i = 0; ok && i < 3; ++i) ok = next_qk();
+                int j = 0, t = (n0 > 0) ? 0 : 1;
+                for (int q = 0; ok && q < total; ++q) {
+                    const int s = j % NST;
+                    stamp(a, tlm, j, 0, 3 * t);
+                    if (t == 0 || j >= n0) {
+                        if (!(ok = wait(&sh.v_full[s], (j / NST) & 1, W_VFULL, j))) break;
                     }
-                    if (!ok) break;
-                    if (j + 1 < n) umma_commit_lead(leader, &sh.k_empty[s1]);
+                    if (!(ok = wait(&sh.p_full[q % 3], (q / 3) & 1, W_PFULL, j))) break;
+                    stamp(a, tlm, j, 0, 1 + 3 * t);
+                    tc_fence_after_sync();
+                    issue_pv(t, s, q % 3, j == 0 && !a.continue_state);
+                    if (t == 1 || j >= n1) umma_commit_lead(leader, &sh.v_empty[s]);
+                    ok = next_qk();
+                    stamp(a, tlm, j, 0, 2 + 3 * t);
+                    advance(j, t);
                 }
             }
         }
@@ -278,7 +298,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         const bool row_ok = qrow < a.Tq;
         const int nt = t == 0 ? n0 : n1;
         const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t tS = trow + COL_S0 + t * TILE;
         const uint32_t tO = trow + COL_O0 + t * HEAD_DIM;
         const bool tls = tl && row == 0;
         // last key index (local to this call's K) this row may see
@@ -314,10 +333,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tmem_wait_st();
         }
 
+        int q_prev = 0;  // number of this tile's previous product
         for (int j = 0; j < nt; ++j) {
             stamp(a, tls, j, 1 + t, 0);
+            // this product's number in the issue order picks its score buffer
+            const int q = min(j, n0) + min(j, n1) + ((t == 1 && j < n0) ? 1 : 0);
+            const uint32_t tS = trow + score_col(q % 3);
             // the vote keeps the warp converged for the .sync.aligned tensor-memory accesses below
-            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.s_full[t], j & 1, W_SFULL, j));
+            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.s_full[q % 3], (q / 3) & 1, W_SFULL, j));
             if (!ok) break;
             stamp(a, tls, j, 1 + t, 1);
             tc_fence_after_sync();
@@ -362,8 +385,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             const float m_new = raise ? m_cand : m;
             const float alpha = raise ? ((m == -INFINITY) ? 0.f : ex2_approx(m - m_cand)) : 1.f;
             if ((j > 0 || a.continue_state) && __any_sync(0xffffffffu, raise)) {
-                // rescale the running output (PV of the previous step has completed: the commit that
-                // released S for this step was issued after it)
+                // rescale the running output, once the P V of the previous step has completed
+                if (j > 0) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.o_full[q_prev % 3], (q_prev / 3) & 1, W_OFULL, j));
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                }
 #pragma unroll 1
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t o[32];
@@ -426,12 +453,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             stamp(a, tls, j, 1 + t, 3);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&sh.p_full[t]);
+            mbar_arrive(&sh.p_full[q % 3]);
+            q_prev = q;
             stamp(a, tls, j, 1 + t, 4);
         }
 
         // epilogue: O / l and LSE
-        if (ok && nt > 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.o_full[t], (nt - 1) & 1, W_OFULL, nt));
+        if (ok && nt > 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.o_full[q_prev % 3], (q_prev / 3) & 1, W_OFULL, nt));
         tc_fence_after_sync();
         const float inv_l = (l > 0.f) ? a.keep_scale / l : 0.f;
         if (ok && nt > 0) {
