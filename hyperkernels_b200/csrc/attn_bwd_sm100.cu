@@ -111,11 +111,14 @@ static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KiB a CTA may opt in to");
 // Timeline slots (SM clock): role r in {0: MMA issuer, 1: compute thread 0}, iteration it, phase ph:
 // buffer[1 + (it * 2 + r) * 8 + ph]; buffer[0] = number of iterations of the recorded CTA.
 #ifdef HK_TIMELINE
+// fixed-cost stamps of the recorded CTA: buffer[3900 + k]
+#define HK_XSTAMP(on, k) do { if (on) a.timeline[3900 + (k)] = clock64(); } while (0)
 __device__ __forceinline__ void stamp(const BwdArgs& a, bool on, int it, int role, int ph) {
     if (on && it < 80) a.timeline[1 + (it * 3 + role) * 16 + ph] = clock64();
 }
 #else
 __device__ __forceinline__ void stamp(const BwdArgs&, bool, int, int, int) {}
+#define HK_XSTAMP(on, k)
 #endif
 
 enum WaitId {
@@ -144,6 +147,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         a.timeline[4 * blockIdx.x] = (long long)globaltimer_ns();
         a.timeline[4 * blockIdx.x + 2] = clock64();
     }
+#ifdef HK_TIMELINE
+    const bool tlx = a.timeline != nullptr && (int)blockIdx.x == a.timeline_block && threadIdx.x == 0;
+#else
+    constexpr bool tlx = false;
+#endif
+    HK_XSTAMP(tlx, 0);
     if ((smem_u32(smem) & 1023u) != 0) {  // never expected; refuse to run on a misplaced buffer
         if (threadIdx.x == 0 && atomicCAS(&a.status->code, 0, 299) == 0) a.status->block = blockIdx.x;
         return;
@@ -177,7 +186,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
     const int n_it = n_qtiles - it0;
 
-    if (threadIdx.x == 0) {
+    // The load warp initialises the barriers its copies complete on and issues the loads of the first tile at once:
+    // the other warps meet those barriers only after the __syncthreads below, and ~1 000 cycles of set-up (the other
+    // barriers, the tensor-memory allocation) run under the latency of the first loads instead of before it.
+    if (warp == W_LOAD && lane == 0) {
         mbar_init(&sh.k_full, 1);
         mbar_init(&sh.v_full, 1);
         mbar_init(&sh.km_full, 1);
@@ -185,6 +197,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         mbar_init(&sh.do_full, 1);
         mbar_init(&sh.qm_full, 1);
         mbar_init(&sh.dom_full, 1);
+        fence_mbar_init();
+        if (n_it > 0) {
+            // in the order the first products need them: K, Q (S^T), V, dO (dP^T), MN-major dO (dV), Q (dK), K (dQ)
+            const int q0 = it0 * TILE;
+            mbar_arrive_expect_tx(&sh.k_full, TILE_BYTES);
+            tma_load_4d(sK, &mapK, &sh.k_full, 0, kv0, h, b);
+            tma_load_4d(sK + BOX_BYTES, &mapK, &sh.k_full, HALF_D, kv0, h, b);
+            mbar_arrive_expect_tx(&sh.q_full, TILE_BYTES);
+            tma_load_4d(sQ, &mapQ, &sh.q_full, 0, q0, h, b);
+            tma_load_4d(sQ + BOX_BYTES, &mapQ, &sh.q_full, HALF_D, q0, h, b);
+            mbar_arrive_expect_tx(&sh.v_full, TILE_BYTES);
+            tma_load_4d(sV, &mapV, &sh.v_full, 0, kv0, h, b);
+            tma_load_4d(sV + BOX_BYTES, &mapV, &sh.v_full, HALF_D, kv0, h, b);
+            mbar_arrive_expect_tx(&sh.do_full, TILE_BYTES);
+            tma_load_4d(sdO, &mapdO, &sh.do_full, 0, q0, h, b);
+            tma_load_4d(sdO + BOX_BYTES, &mapdO, &sh.do_full, HALF_D, q0, h, b);
+            mbar_arrive_expect_tx(&sh.dom_full, TILE_BYTES);
+            tma_load_4d(sdOm, &mapdOm, &sh.dom_full, 0, q0, h, b);
+            tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.dom_full, HALF_D, q0, h, b);
+            mbar_arrive_expect_tx(&sh.qm_full, TILE_BYTES);
+            tma_load_4d(sQm, &mapQm, &sh.qm_full, 0, q0, h, b);
+            tma_load_4d(sQm + BOX_BYTES, &mapQm, &sh.qm_full, HALF_D, q0, h, b);
+            mbar_arrive_expect_tx(&sh.km_full, TILE_BYTES);
+            tma_load_4d(sKm, &mapKm, &sh.km_full, 0, kv0, h, b);
+            tma_load_4d(sKm + BOX_BYTES, &mapKm, &sh.km_full, HALF_D, kv0, h, b);
+        }
+    }
+    if (threadIdx.x == 0) {
         mbar_init(&sh.v_ready, NUM_COMPUTE);
         mbar_init(&sh.qk_free, 1);
         mbar_init(&sh.dok_free, 1);
@@ -221,19 +261,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     constexpr bool tl = false;
 #endif
     if (tl && threadIdx.x == 0) a.timeline[0] = n_it;
+    HK_XSTAMP(tlx, 1);
 
     if (warp == W_LOAD) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0 && n_it > 0) {
-            tma_prefetch_desc(&mapQ);
-            tma_prefetch_desc(&mapK);
-            tma_prefetch_desc(&mapV);
-            tma_prefetch_desc(&mapdO);
-            tma_prefetch_desc(&mapQm);
-            tma_prefetch_desc(&mapKm);
-            tma_prefetch_desc(&mapdOm);
-            // in the order the first products need them: K, Q (S^T), V, dO (dP^T), MN-major dO (dV), Q (dK), K (dQ)
-            int issued_q = 0, issued_do = 0, issued_qm = 0, issued_dom = 0;
+            // the loads of the first tile were issued before the set-up barrier
+            int issued_q = 1, issued_do = 1, issued_qm = 1, issued_dom = 1;
             auto load_q = [&](int q0) {
                 mbar_arrive_expect_tx(&sh.q_full, TILE_BYTES);
                 tma_load_4d(sQ, &mapQ, &sh.q_full, 0, q0, h, b);
@@ -258,19 +292,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tma_load_4d(sdOm + BOX_BYTES, &mapdOm, &sh.dom_full, HALF_D, q0, h, b);
                 ++issued_dom;
             };
-            mbar_arrive_expect_tx(&sh.k_full, TILE_BYTES);
-            tma_load_4d(sK, &mapK, &sh.k_full, 0, kv0, h, b);
-            tma_load_4d(sK + BOX_BYTES, &mapK, &sh.k_full, HALF_D, kv0, h, b);
-            load_q(it0 * TILE);
-            mbar_arrive_expect_tx(&sh.v_full, TILE_BYTES);
-            tma_load_4d(sV, &mapV, &sh.v_full, 0, kv0, h, b);
-            tma_load_4d(sV + BOX_BYTES, &mapV, &sh.v_full, HALF_D, kv0, h, b);
-            load_do(it0 * TILE);
-            load_dom(it0 * TILE);
-            load_qm(it0 * TILE);
-            mbar_arrive_expect_tx(&sh.km_full, TILE_BYTES);
-            tma_load_4d(sKm, &mapKm, &sh.km_full, 0, kv0, h, b);
-            tma_load_4d(sKm + BOX_BYTES, &mapKm, &sh.km_full, HALF_D, kv0, h, b);
             bool tok = true;
             for (int it = 0; it + 1 < n_it; ++it) {
                 const int q1 = (it0 + it + 1) * TILE;
@@ -425,7 +446,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 return true;
             };
             bool tok = true;
-            for (int j = 0; tok && j + 1 < n_it; ++j) tok = reduce_dq(j);  // the last tile's dQ leaves from registers
+            for (int j = 0; tok && j + 1 < n_it; ++j) tok = reduce_dq(j);  // the last tile's dQ follows dV and dK
             // dV and dK, staged by the compute warps in the MN-major Q tile and the K-major K tile (dead after the last
             // dK and S^T): stored -- added, if the caller accumulates -- with bulk copies; a thread-per-row store would
             // be 32 lines per instruction
@@ -442,9 +463,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     tma_store_4d(&mapdK, sK + BOX_BYTES, HALF_D, kv0, h, b);
                 }
                 bulk_commit_group();
+                tok = reduce_dq(n_it - 1);
             }
             // the copies have read their shared-memory sources; they complete on their own
             bulk_wait_group_read_all();
+            HK_XSTAMP(tl, 8);
         }
     } else {
         // ------------------------------ compute ------------------------------
@@ -504,6 +527,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         // columns, read from the 128-byte-swizzled landing buffer (16-byte chunk c of row r at position c ^ (r & 7))
         if (n_it > 0) {
             ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.v_full, 0, W_KVFULL, 3));
+            HK_XSTAMP(tlx, 2);
             if (ok) {
                 uint32_t rv[16];
                 const uint8_t* vrow = sV + (part >> 1) * BOX_BYTES + row * 128;
@@ -517,6 +541,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tc_fence_before_sync();
                 mbar_arrive(&sh.v_ready);
             }
+            HK_XSTAMP(tlx, 3);
         }
 
         for (int it = 0; ok && it < n_it; ++it) {
@@ -722,7 +747,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         // pipe).  Column groups 0,1 put dV (times 1/(1-p) for inverted dropout) into the MN-major Q tile and groups
         // 2,3 dK into the K-major K tile, both dead by then, as the boxes of a 128-byte-swizzled TMA tile: 16-byte
         // chunk c of row r at position c ^ (r & 7).
+        HK_XSTAMP(tlx, 4);
         if (ok && n_it > 0) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dk_done, (n_it - 1) & 1, W_BDONE, n_it));
+        HK_XSTAMP(tlx, 5);
         if (ok && n_it > 0) {
             tc_fence_after_sync();
             tmem_ld32(trow + ((part < 2) ? COL_DV + part * 32 : COL_DK + (part - 2) * 32), rs);
@@ -736,6 +763,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                                 __uint_as_float(rs[4 * c + 2]) * f, __uint_as_float(rs[4 * c + 3]) * f);
             fence_proxy_async_smem();
             mbar_arrive(&sh.acc_staged);
+            HK_XSTAMP(tlx, 6);
         } else if (n_it == 0 && kv_ok && !a.accum_dkdv) {
             // no query sees this KV tile: its dK and dV rows are zero
             float* out_row = (part < 2)
@@ -745,28 +773,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(out_row + i) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
 
-        // dQ of the last query tile: nothing is left to overlap a bulk reduction with (it keeps its shared-memory
-        // source for ~1 600 cycles, and the CTA could not end before), so it goes from tensor memory to global memory
-        // through registers, in the accumulator-fragment shape (four threads hold 32 consecutive bytes of a row):
-        // column group 2 takes the first 16 lanes of its warp's quarter, group 3 the other 16.  The additions
-        // complete on their own after the CTA has gone.
+        // dQ of the last query tile takes the same way out as the others: staged in the K-major dO tile (dead: its
+        // last reader was dP^T of this tile) once the reduction of the previous tile has read that buffer, then
+        // added to global memory by the store warp.  (From registers with red.global.add it took ~2 500 cycles per
+        // CTA and held up the bulk stores of dV and dK behind it.)
         if (ok && n_it > 0 && part >= 2) {
-            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_full, (n_it - 1) & 1, W_DQFULL, n_it - 1));
-            if (ok) {
-                tc_fence_after_sync();
-                tmem_ld_16x256b_x8(tmem + ((uint32_t)(quarter * 32 + 16 * (part & 1)) << 16) + COL_DQ, rs);
-                tmem_wait_ld();
-                const int q0j = (it0 + n_it - 1) * TILE;
-                const int ra = quarter * 32 + 16 * (part & 1) + (lane >> 2);
-                float* gA = a.dQ + (int64_t)b * a.dq_sB + (int64_t)h * a.dq_sH + (int64_t)(q0j + ra) * a.dq_sM + 2 * (lane & 3);
-                float* gB = gA + 8 * a.dq_sM;
-                const bool okA = q0j + ra < a.Tq, okB = q0j + ra + 8 < a.Tq;
-#pragma unroll
-                for (int jg = 0; jg < 8; ++jg) {
-                    if (okA) red_add_v2(gA + 8 * jg, rs[4 * jg], rs[4 * jg + 1]);
-                    if (okB) red_add_v2(gB + 8 * jg, rs[4 * jg + 2], rs[4 * jg + 3]);
-                }
-            }
+            if (n_it > 1) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dq_out, (n_it - 2) & 1, W_DQOUT, n_it - 2));
+            if (ok) ok = drain_dq(n_it - 1, rs);
+            HK_XSTAMP(tl && tid == 256, 9);
         }
 
     }
@@ -774,6 +788,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     // ------------------------------ teardown ------------------------------
     tc_fence_before_sync();
     __syncthreads();
+    HK_XSTAMP(tlx, 7);
     if (warp == W_MMA) {
         __syncwarp();
         tc_fence_after_sync();

@@ -133,12 +133,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const int n1 = kv_tiles_for(a, q0 + TILE);
     const int n = max(n0, n1);
 
-    if (threadIdx.x == 0) {
+    // The producer initialises the barriers its copies complete on and issues the first loads at once (Q, and the
+    // first NST key/value tiles, which wait for no consumer): the rest of the set-up -- the other barriers, the
+    // tensor-memory allocation -- runs under their latency.  The other warps meet these barriers only after the
+    // __syncthreads below.
+    if (warp == 0 && lane == 0) {
         mbar_init(&sh.q_full, 1);
         for (int s = 0; s < NST; ++s) {
             mbar_init(&sh.k_full[s], 1);
-            mbar_init(&sh.k_empty[s], 1);
             mbar_init(&sh.v_full[s], 1);
+        }
+        fence_mbar_init();
+        if (n > 0) {
+            mbar_arrive_expect_tx(&sh.q_full, 2 * TILE_BYTES);
+            for (int t = 0; t < 2; ++t) {
+                tma_load_4d(sQ + t * TILE_BYTES, &mapQ, &sh.q_full, 0, q0 + t * TILE, h, b);
+                tma_load_4d(sQ + t * TILE_BYTES + BOX_BYTES, &mapQ, &sh.q_full, HALF_D, q0 + t * TILE, h, b);
+            }
+            for (int j = 0; j < n && j < NST; ++j) {
+                mbar_arrive_expect_tx(&sh.k_full[j], TILE_BYTES);
+                tma_load_4d(sK + j * TILE_BYTES, &mapK, &sh.k_full[j], 0, j * TILE, h, b);
+                tma_load_4d(sK + j * TILE_BYTES + BOX_BYTES, &mapK, &sh.k_full[j], HALF_D, j * TILE, h, b);
+                mbar_arrive_expect_tx(&sh.v_full[j], TILE_BYTES);
+                tma_load_4d(sV + j * TILE_BYTES, &mapV, &sh.v_full[j], 0, j * TILE, h, b);
+                tma_load_4d(sV + j * TILE_BYTES + BOX_BYTES, &mapV, &sh.v_full[j], HALF_D, j * TILE, h, b);
+            }
+        }
+    }
+    if (threadIdx.x == 64) {  // an idle warp takes the rest of the barriers
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(&sh.k_empty[s], 1);
             mbar_init(&sh.v_empty[s], 1);
         }
         // The score barriers belong to the score BUFFER, not to the tile: the warps of a tile may be a whole step
@@ -173,16 +197,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         if (warp == 0) {
             // ------------------------------ TMA producer ------------------------------
             if (lane == 0 && n > 0) {
-                tma_prefetch_desc(&mapQ);
-                tma_prefetch_desc(&mapK);
-                tma_prefetch_desc(&mapV);
-                mbar_arrive_expect_tx(&sh.q_full, 2 * TILE_BYTES);
-                for (int t = 0; t < 2; ++t) {
-                    tma_load_4d(sQ + t * TILE_BYTES, &mapQ, &sh.q_full, 0, q0 + t * TILE, h, b);
-                    tma_load_4d(sQ + t * TILE_BYTES + BOX_BYTES, &mapQ, &sh.q_full, HALF_D, q0 + t * TILE, h, b);
-                }
-                int issued = 0;
-                for (int j = 0; j < n; ++j) {
+                // Q and the first NST key/value tiles were issued before the set-up barrier
+                int issued = min(n, NST);
+                for (int j = NST; j < n; ++j) {
                     const int s = j % NST;
                     const uint32_t par = ((j / NST) - 1) & 1;
                     if (j >= NST && !mbar_wait(wc, &sh.k_empty[s], par, W_KEMPTY, j)) break;
