@@ -2,9 +2,12 @@
 
 The reference has no multi-GPU path at all; this module is the host-side schedule
 that shards ONE attention problem over the sequence: every rank keeps its slice
-of Q (and of O, LSE, dO, dQ) and the K/V slices travel round the ring with
-``torch.distributed`` send/recv (NCCL over NVLink on GPUs), one hop per step,
-overlapped with the compute of the step.  The compute of a step is a plain call
+of Q (and of O, LSE, dO, dQ) and the K/V slices travel round the ring, one hop
+per step, overlapped with the compute of the step.  On GPUs a hop is one call of
+the native transport ``libhk_ring.so`` (include/hk_ring.h: ncclSend + ncclRecv in
+one group on a communication stream, ordered against the compute stream with
+events inside the call); on CPU ranks, or when that library is absent, it is
+``torch.distributed`` batched isend/irecv.  The compute of a step is a plain call
 of the single-GPU kernels through the C ABI on a (query segment, key segment)
 pair, told where the two segments sit in the global sequence
 (``q_pos0``/``k_pos0``).  In the forward the running result of a query segment is
@@ -25,6 +28,8 @@ product backend is ``CudaBackend`` and needs the compiled library and a GPU.
 """
 from __future__ import annotations
 
+import ctypes
+import os
 from typing import List, Tuple
 
 import torch
@@ -91,6 +96,66 @@ class RingError(RuntimeError):
     """A hop of the ring did not complete: a peer failed, never joined, or the exchange timed out."""
 
 
+class NativeTransport:
+    """The hop through libhk_ring.so (include/hk_ring.h): its own NCCL communicator over the ranks of the ring,
+    created from a unique id that ring rank 0 makes and the process group broadcasts."""
+
+    SLOTS = 4
+
+    def __init__(self, group, rank: int, world: int):
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libhk_ring.so")
+        L = ctypes.CDLL(path)
+        L.hk_ring_get_unique_id.argtypes = [ctypes.c_void_p]
+        L.hk_ring_create.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+        L.hk_ring_exchange.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                       ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
+        L.hk_ring_join.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        L.hk_ring_wait.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_double]
+        L.hk_ring_poll.argtypes = [ctypes.c_void_p]
+        L.hk_ring_destroy.argtypes = [ctypes.c_void_p]
+        L.hk_ring_abort.argtypes = [ctypes.c_void_p]
+        L.hk_ring_error_string.restype = ctypes.c_char_p
+        L.hk_ring_error_string.argtypes = [ctypes.c_int]
+        L.hk_ring_last_nccl_error.restype = ctypes.c_char_p
+        self.L, self.rank, self.world = L, rank, world
+        uid = ctypes.create_string_buffer(128)
+        if rank == 0:
+            self._check(L.hk_ring_get_unique_id(uid), "unique id")
+        box = [uid.raw]
+        src = dist.get_global_rank(group, 0) if group is not None else 0
+        dist.broadcast_object_list(box, src=src, group=group)
+        uid = ctypes.create_string_buffer(box[0], 128)
+        self.ring = ctypes.c_void_p()
+        self._check(L.hk_ring_create(ctypes.byref(self.ring), uid, rank, world), "communicator")
+        self.next_slot = 0
+
+    def _check(self, rc: int, what: str):
+        if rc != 0:
+            raise RingError(f"ring rank {self.rank}: {what}: {self.L.hk_ring_error_string(rc).decode()} "
+                            f"({self.L.hk_ring_last_nccl_error().decode()})")
+
+    def exchange(self, send, recv, compute_stream, comm_stream) -> int:
+        """Posts send -> next rank, recv <- previous rank; returns the hop's slot."""
+        assert send.is_contiguous() and recv.is_contiguous() and send.numel() == recv.numel()
+        slot = self.next_slot
+        self.next_slot = (slot + 1) % self.SLOTS
+        self._check(self.L.hk_ring_exchange(self.ring, slot, send.data_ptr(), (self.rank + 1) % self.world, recv.data_ptr(),
+                                            (self.rank - 1) % self.world, send.numel() * send.element_size(),
+                                            compute_stream.cuda_stream, comm_stream.cuda_stream), "hop")
+        return slot
+
+    def finish(self, slot: int, compute_stream, timeout_s):
+        if timeout_s is not None:
+            self._check(self.L.hk_ring_wait(self.ring, slot, float(timeout_s)), "hop")
+        self._check(self.L.hk_ring_join(self.ring, slot, compute_stream.cuda_stream), "join")
+
+    def close(self, abort: bool = False):
+        """abort=True after a failed hop or when a peer may be gone: never blocks on the other ranks."""
+        if self.ring:
+            (self.L.hk_ring_abort if abort else self.L.hk_ring_destroy)(self.ring)
+            self.ring = ctypes.c_void_p()
+
+
 class RingAttention:
     """Attention of a sequence of length T sharded over the ranks of `group`.
 
@@ -99,11 +164,13 @@ class RingAttention:
     """
 
     def __init__(self, T: int, scale: float, causal: bool, group=None, layout: str = "zigzag", backend=None,
-                 timeout_s: float = None):
+                 timeout_s: float = None, transport: str = "auto"):
         """timeout_s: if set, every hop is waited for on the HOST with this limit and a hop that does not complete
         raises RingError (failure detection for a peer that died or never joined; it costs the overlap of the host
         with the GPU).  If None, completion is ordered on the stream only and a lost peer surfaces through the
-        process group's own timeout (NCCL watchdog)."""
+        process group's own timeout (NCCL watchdog).
+        transport: "native" (libhk_ring.so), "torch" (torch.distributed isend/irecv) or "auto" (native with the CUDA
+        backend on a ring of more than one rank, torch otherwise)."""
         self.timeout_s = timeout_s
         self.group = group
         self.rank = dist.get_rank(group)
@@ -112,6 +179,9 @@ class RingAttention:
         self.backend = backend if backend is not None else CudaBackend()
         self.my_segs = segments_of(self.rank, self.world, T, layout)
         self.comm_stream = torch.cuda.Stream() if torch.cuda.is_available() and backend is None else None
+        if transport == "auto":
+            transport = "native" if (self.comm_stream is not None and self.world > 1) else "torch"
+        self.native = NativeTransport(group, self.rank, self.world) if transport == "native" else None
 
     # ---- plumbing ---------------------------------------------------------------
     def _peer(self, offset: int) -> int:
@@ -125,6 +195,8 @@ class RingAttention:
         return dist.batch_isend_irecv(ops)
 
     def _start_exchange(self, send_buf, recv_buf):
+        if self.native is not None:
+            return self.native.exchange(send_buf, recv_buf, torch.cuda.current_stream(), self.comm_stream), "native"
         if self.comm_stream is None:
             try:
                 return self._exchange(send_buf, recv_buf), None
@@ -141,6 +213,9 @@ class RingAttention:
 
     def _finish(self, handle):
         reqs, stream = handle
+        if stream == "native":
+            self.native.finish(reqs, torch.cuda.current_stream(), self.timeout_s)
+            return
         try:
             for r in reqs:
                 if self.timeout_s is not None:

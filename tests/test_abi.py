@@ -161,3 +161,26 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(att, "_LIB_PATH", "/nonexistent/libhk_attention.so")
     with pytest.raises(ImportError):
         att.lib()
+
+
+def test_ring_library_loads_and_exports_every_symbol():
+    """libhk_ring.so (include/hk_ring.h): every declared function is exported; without a GPU the communicator cannot be
+    made and the call says so with a status code instead of crashing."""
+    import ctypes as C
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = open(os.path.join(root, "include", "hk_ring.h")).read()
+    names = sorted(set(re.findall(r"\b(hk_ring_[a-z_]+)\s*\(", header)))
+    assert len(names) >= 9
+    L = C.CDLL(os.path.join(root, "hyperkernels_b200", "lib", "libhk_ring.so"))
+    for n in names:
+        assert hasattr(L, n), n
+    L.hk_ring_error_string.restype = C.c_char_p
+    assert L.hk_ring_error_string(0) == b"ok"
+    assert L.hk_ring_get_unique_id(None) == -4
+    ring = C.c_void_p()
+    uid = C.create_string_buffer(128)
+    assert L.hk_ring_create(C.byref(ring), uid, 3, 2) == -4  # rank outside the ring
+    assert L.hk_ring_exchange(None, 0, None, 0, None, 0, 0, None, None) == -4
+    assert L.hk_ring_wait(None, 0, C.c_double(0.1)) == -4

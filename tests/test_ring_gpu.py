@@ -15,7 +15,7 @@ sys.path.insert(0, os.path.dirname(HERE))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, layout, T, ret):
+def _worker(rank, world, port, layout, T, ret, transport="auto"):
     import torch.distributed as dist
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -32,7 +32,8 @@ def _worker(rank, world, port, layout, T, ret):
         K[:, :, ::64] *= 2.0
         segs = segments_of(rank, world, T, layout)
         shard = lambda x: torch.cat([x[:, :, s:s + n] for (s, n) in segs], dim=2).contiguous()
-        ring = RingAttention(T, 0.125, True, layout=layout)
+        ring = RingAttention(T, 0.125, True, layout=layout, transport=transport)
+        assert (ring.native is not None) == (transport != "torch")
         O_l, L_l = ring.forward(shard(Q), shard(K), shard(V))
         dQ_l, dK_l, dV_l = ring.backward(shard(Q), shard(K), shard(V), O_l, L_l, shard(dO))
         torch.cuda.synchronize()
@@ -50,15 +51,17 @@ def _worker(rank, world, port, layout, T, ret):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("transport", ["native", "torch"])
 @pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
-def test_ring_matches_single_gpu(layout):
+def test_ring_matches_single_gpu(layout, transport):
+    """transport: the hop through libhk_ring.so (one native call per hop) or through torch.distributed."""
     import torch.multiprocessing as mp
 
     world = 2
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
-    port = 29800 + (7 if layout == "zigzag" else 0)
-    procs = [ctx.Process(target=_worker, args=(r, world, port, layout, 1024, ret)) for r in range(world)]
+    port = 29800 + (7 if layout == "zigzag" else 0) + (20 if transport == "torch" else 0)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, layout, 1024, ret, transport)) for r in range(world)]
     for p in procs:
         p.start()
     results = [ret.get(timeout=300) for _ in range(world)]
@@ -70,3 +73,62 @@ def test_ring_matches_single_gpu(layout):
         # gate of the oracle, so within twice that of each other
         for i in range(0, len(errs), 2):
             assert errs[i] <= 1e-2 and errs[i + 1] <= 2e-3, (rank, errs)
+
+
+def _timeout_worker(rank, world, port, ret):
+    """Rank 1 never posts its side of the hop; rank 0's host-side wait gives up after its limit, takes its
+    communicator down (ncclCommAbort) and raises RingError.  Nobody dies and no rank leaves with work in flight."""
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from hyperkernels_b200.ring import NativeTransport, RingError
+
+        tr = NativeTransport(None, rank, world)
+        a = torch.ones(1 << 20, device="cuda")
+        b = torch.zeros(1 << 20, device="cuda")
+        comm = torch.cuda.Stream()
+        # one good hop first: both sides post
+        slot = tr.exchange(a, b, torch.cuda.current_stream(), comm)
+        tr.finish(slot, torch.cuda.current_stream(), 30.0)
+        torch.cuda.synchronize()
+        assert float(b.sum()) == float(1 << 20)
+        outcome = "idle"
+        if rank == 0:
+            slot = tr.exchange(a, b, torch.cuda.current_stream(), comm)
+            try:
+                tr.finish(slot, torch.cuda.current_stream(), 1.5)
+                outcome = "completed"
+            except RingError as e:
+                outcome = "RingError: " + str(e)
+            torch.cuda.synchronize()  # the aborted hop has left the stream: the context is usable
+            assert float((a + 1).sum()) == float(2 << 20)
+        ret.put((rank, outcome))
+        ret.close()
+        ret.join_thread()
+        dist.barrier()  # rank 1 waits here, on the process group, while rank 0 times out
+        tr.close(abort=True)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_native_hop_that_never_completes_raises_ring_error():
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_timeout_worker, args=(r, world, 29871, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(ret.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results[0].startswith("RingError") and "did not complete in time" in results[0], results
+    assert results[1] == "idle"
