@@ -421,18 +421,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
             if (a.dropout_mode == 0) {
+                // two scores per FMA and per add (fma.rn.f32x2 / add.rn.f32x2: the same roundings as the scalar forms)
+                const float2 c2 = make_float2(c, c), nm2 = make_float2(neg_m, neg_m);
+                float2 s01 = make_float2(0.f, 0.f), s23 = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int i = 0; i < 128; i += 4) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), c, neg_m));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), c, neg_m));
-                    const float p2 = ex2_approx(fmaf(__uint_as_float(r[i + 2]), c, neg_m));
-                    const float p3 = ex2_approx(fmaf(__uint_as_float(r[i + 3]), c, neg_m));
-                    s0 += p0; s1 += p1; s2 += p2; s3 += p3;
-                    r[i] = tf32_round_bits_mma(__float_as_uint(p0));
-                    r[i + 1] = tf32_round_bits_mma(__float_as_uint(p1));
-                    r[i + 2] = tf32_round_bits_mma(__float_as_uint(p2));
-                    r[i + 3] = tf32_round_bits_mma(__float_as_uint(p3));
+                    const float2 t01 = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c2, nm2);
+                    const float2 t23 = __ffma2_rn(make_float2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), c2, nm2);
+                    const float2 p01 = make_float2(ex2_approx(t01.x), ex2_approx(t01.y));
+                    const float2 p23 = make_float2(ex2_approx(t23.x), ex2_approx(t23.y));
+                    s01 = __fadd2_rn(s01, p01);
+                    s23 = __fadd2_rn(s23, p23);
+                    r[i] = tf32_round_bits_mma(__float_as_uint(p01.x));
+                    r[i + 1] = tf32_round_bits_mma(__float_as_uint(p01.y));
+                    r[i + 2] = tf32_round_bits_mma(__float_as_uint(p23.x));
+                    r[i + 3] = tf32_round_bits_mma(__float_as_uint(p23.y));
                 }
+                s0 = s01.x; s1 = s01.y; s2 = s23.x; s3 = s23.y;
             } else if (a.dropout_mode == 2) {
                 // one Philox call per eight keys of this row
 #pragma unroll
