@@ -438,14 +438,15 @@ def run_ours(args, cfg, rank, local_rank, world):
             "config": {"workload": cfg["name"] + (" per GPU" if world > 1 and args.scaling == "weak" else ""),
                        "config_id": args.config,
                        "l2": "256 MiB buffer written before every timed sample (untimed)",
-                       "step": "hk_attn_forward + hk_attn_backward (TF32 rounding pre-pass once per step, D pre-pass + dQ zeroing, main kernels), captured in a CUDA graph and replayed",
+                       "step": "hk_attn_forward + hk_attn_backward with every launch they make (operand rounding to TF32: in shared memory inside the kernels for 512 <= N <= 2048 causal / 1024 otherwise, else one HBM pre-pass per step; D pre-pass with dO rounding and dQ zeroing; the two main kernels), captured in a CUDA graph and replayed",
+                       "launches_per_step": int(gstep.launches_per_replay),
                        "timing": f"median of {len(samples)} samples ({args.steps} steps x {inner} replays), one CUDA-event pair per replay",
                        "partition": "batch x head across GPUs, no collective"},
             "ms_per_step_mean": ms_mean,
             "pct_of_tf32_peak": total / world / (ms * 1e-3) / 1e12 / peaks["tf32_tflops"],
             "fwd_tflops": f_fwd / (ms_fwd_call * 1e-3) / 1e12, "bwd_tflops": f_bwd / (ms_bwd_call * 1e-3) / 1e12,
             "call_ms": {"hk_attn_forward": ms_fwd_call, "hk_attn_backward": ms_bwd_call,
-                        "note": "every launch of the call: fwd = Q/K/V rounding pre-pass + forward kernel; bwd = D pre-pass (dO rounding, dQ zeroing) + backward kernel"},
+                        "note": "every launch of the call: fwd = Q/K/V rounding pre-pass (if the config takes the HBM path) + forward kernel; bwd = D pre-pass (dO rounding, dQ zeroing) + backward kernel"},
             "kernel_ms": {"fwd_kernel": k_fwd, "bwd_kernel": k_bwd,
                           "fwd_kernel_tflops": f_fwd / (k_fwd * 1e-3) / 1e12 if k_fwd else None,
                           "bwd_kernel_tflops": achieved},

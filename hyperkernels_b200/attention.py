@@ -39,6 +39,7 @@ FLAG_D_PRECOMPUTED = 1 << 4
 FLAG_REUSE_FWD_ROUNDED = 1 << 5
 FLAG_DROPOUT_SCALED = 1 << 6  # inverted dropout (kept terms / (1 - p), normaliser over all keys)
 FLAG_CONTINUE_SOFTMAX_STATE = 1 << 7  # forward: O, LSE hold the result over earlier keys; fold this call's keys in
+FLAG_ROUND_IN_HBM = 1 << 8  # always round operands with the HBM pre-pass (default: in shared memory for short sequences)
 
 _f32p = C.POINTER(C.c_float)
 
@@ -231,7 +232,7 @@ def _workspace(nbytes: int, like, workspace):
 def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float = 0.0, dropout_mask=None,
                       philox_seed: Optional[int] = None, philox_offset: int = 0, q_pos0: int = 0, k_pos0: int = 0,
                       bh_pos0: int = 0, prerounded: bool = False, dropout_scaled: bool = False, continue_state: bool = False,
-                      workspace=None, out=None, lse=None, stream=None):
+                      round_in_hbm: bool = False, workspace=None, out=None, lse=None, stream=None):
     """O, LSE = fused attention forward of [B,H,Tq,64] Q against [B,H,Tk,64] K, V (fp32 CUDA tensors)."""
     import torch
 
@@ -260,10 +261,20 @@ def attention_forward(Q, K, V, scale: float, causal: bool, *, dropout_p: float =
     if continue_state:
         assert out is not None and lse is not None, "continue_state folds new keys into the given out / lse"
         flags |= FLAG_CONTINUE_SOFTMAX_STATE
+    if round_in_hbm:
+        flags |= FLAG_ROUND_IN_HBM
     p.flags = flags
-    ws = _workspace(fwd_workspace_bytes(p), Q, workspace)
-    if ws is not None:
-        p.workspace, p.workspace_bytes = ws[1], fwd_workspace_bytes(p)
+    need = fwd_workspace_bytes(p)
+    if need == 0 and workspace is not None and not prerounded:
+        # nothing is required (operands rounded in shared memory), but a workspace that is given receives the rounded
+        # Q for a backward call with reuse_fwd_rounded
+        base = workspace.data_ptr()
+        off = (-base) % 256
+        p.workspace, p.workspace_bytes = base + off, workspace.numel() - off
+    else:
+        ws = _workspace(need, Q, workspace)
+        if ws is not None:
+            p.workspace, p.workspace_bytes = ws[1], need
     fused_attn_forward(p, stream)
     return O, LSE
 
@@ -272,7 +283,7 @@ def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropo
                        philox_seed: Optional[int] = None, philox_offset: int = 0, q_pos0: int = 0, k_pos0: int = 0,
                        bh_pos0: int = 0, prerounded: bool = False, D=None, d_precomputed: bool = False, accum_dkdv: bool = False,
                        accum_dq: bool = False, reuse_fwd_rounded: bool = False, dropout_scaled: bool = False,
-                       workspace=None, dQ=None, dK=None, dV=None, stream=None):
+                       round_in_hbm: bool = False, workspace=None, dQ=None, dK=None, dV=None, stream=None):
     """dQ, dK, dV, D = fused attention backward (fp32 CUDA tensors, [B,H,T,64])."""
     import torch
 
@@ -316,6 +327,8 @@ def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropo
     if reuse_fwd_rounded:
         assert workspace is not None, "reuse_fwd_rounded needs the workspace the forward used"
         flags |= FLAG_REUSE_FWD_ROUNDED
+    if round_in_hbm:
+        flags |= FLAG_ROUND_IN_HBM
     p.flags = flags
     ws = _workspace(bwd_workspace_bytes(p), Q, workspace)
     if ws is not None:

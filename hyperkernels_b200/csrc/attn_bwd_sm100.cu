@@ -78,6 +78,7 @@ struct __align__(16) Shared {
     float lse[2][TILE];   // -LSE * log2e of the query tile (-inf for rows past the end), double-buffered
     float dsum[2][TILE];  // -D * scale of the query tile
     uint64_t k_full, v_full, km_full, q_full, do_full, qm_full, dom_full;  // TMA loads
+    uint64_t k_round, km_round;  // round_kv: the compute warps have rounded the K-major / MN-major K tile in place
     uint64_t v_ready;       // V is in tensor memory (and its landing buffer is free)
     uint64_t qk_free, dok_free;  // S^T(i) / dP^T(i) complete: the K-major Q / dO tile may be refilled
     uint64_t s_full, dp_full;
@@ -226,6 +227,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
     if (threadIdx.x == 0) {
         mbar_init(&sh.v_ready, NUM_COMPUTE);
+        mbar_init(&sh.k_round, NUM_COMPUTE);
+        mbar_init(&sh.km_round, NUM_COMPUTE);
         mbar_init(&sh.qk_free, 1);
         mbar_init(&sh.dok_free, 1);
         mbar_init(&sh.s_full, 1);
@@ -336,7 +339,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                            dom_addr = smem_u32(sdOm), km_addr = smem_u32(sKm), ds_addr = smem_u32(sdS);
             // S^T of query tile `it` (local index) as soon as K and Q have landed; the exponentials need nothing else
             auto issue_st = [&](int it) -> bool {
-                if (it == 0 && !wait(&sh.k_full, 0, W_KVFULL, 0)) return false;
+                if (it == 0 && !wait(a.round_kv ? &sh.k_round : &sh.k_full, 0, W_KVFULL, 0)) return false;
                 if (!wait(&sh.q_full, it & 1, W_QKFULL, it)) return false;
                 tc_fence_after_sync();
 #pragma unroll
@@ -400,7 +403,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 // dQ = dS K once dS is staged (shortly after dS^T was stored) and the previous dQ has left tensor memory
                 if (!(ok = wait(&sh.ds_ready, par, W_DSREADY, it))) break;
                 if (it > 0 && !(ok = wait(&sh.dq_empty, (it - 1) & 1, W_DQEMPTY, it))) break;
-                if (it == 0 && !(ok = wait(&sh.km_full, 0, W_KVFULL, 2))) break;
+                if (it == 0 && !(ok = wait(a.round_kv ? &sh.km_round : &sh.km_full, 0, W_KVFULL, 2))) break;
                 stamp(a, tlm, it, 0, 5);
                 tc_fence_after_sync();
 #pragma unroll
@@ -525,8 +528,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 
         // V of this KV tile into tensor memory (A operand of dP^T = V dO^T): this thread's key row, 16 of the 64
         // columns, read from the 128-byte-swizzled landing buffer (16-byte chunk c of row r at position c ^ (r & 7))
+        // round_kv (short sequences, decided by the host): K and V come straight from the caller's tensors and are
+        // rounded to TF32 by the compute warps, once per CTA -- the K-major K tile first (S^T of the first tile waits for
+        // it), V on its way into tensor memory, the MN-major K tile inside the first tile (the first dQ needs it).  Same function as the HBM
+        // pre-pass, so the results are bit-identical to that path.
+        auto round_k_tile = [&](uint8_t* tile) {
+            uint4* p4 = reinterpret_cast<uint4*>(tile);
+#pragma unroll
+            for (int k = 0; k < TILE_BYTES / 16 / NUM_COMPUTE; ++k) {
+                uint4 x = p4[tid + k * NUM_COMPUTE];
+                x.x = tf32_round_bits(x.x); x.y = tf32_round_bits(x.y);
+                x.z = tf32_round_bits(x.z); x.w = tf32_round_bits(x.w);
+                p4[tid + k * NUM_COMPUTE] = x;
+            }
+            fence_proxy_async_smem();
+        };
         if (n_it > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.v_full, 0, W_KVFULL, 3));
+            if (a.round_kv) {
+                ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.k_full, 0, W_KVFULL, 4));
+                if (ok) {
+                    round_k_tile(sK);
+                    mbar_arrive(&sh.k_round);
+                }
+            }
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.v_full, 0, W_KVFULL, 3));
             HK_XSTAMP(tlx, 2);
             if (ok) {
                 uint32_t rv[16];
@@ -535,6 +560,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 for (int c = 0; c < 4; ++c) {
                     const uint4 x = *reinterpret_cast<const uint4*>(vrow + (((4 * (part & 1) + c) ^ (row & 7)) << 4));
                     rv[4 * c] = x.x; rv[4 * c + 1] = x.y; rv[4 * c + 2] = x.z; rv[4 * c + 3] = x.w;
+                }
+                if (a.round_kv) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) rv[i] = tf32_round_bits(rv[i]);
                 }
                 tmem_st16(trow + COL_V + 16 * part, rv);
                 tmem_wait_st();
@@ -666,6 +695,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 tmem_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(&sh.pt_ready[part]);
+            }
+            if (it == 0 && a.round_kv) {
+                // the MN-major K tile (last of the first loads, first read by dQ of this tile): rounded here, where
+                // the warps would otherwise wait for dP^T
+                ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.km_full, 0, W_KVFULL, 5));
+                if (!ok) break;
+                round_k_tile(sKm);
+                mbar_arrive(&sh.km_round);
             }
             ok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.dp_full, it & 1, W_SFULL, 1000 + it));
             if (!ok) break;

@@ -53,6 +53,8 @@ constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 struct __align__(8) Shared {
     uint64_t q_full, k_full[NST], k_empty[NST], v_full[NST], v_empty[NST], s_full[3], p_full[3], o_full[3];
+    // round_in_smem: warps 2, 3 have rounded the landed tile to TF32; the rounded Q tiles have been read by their store
+    uint64_t q_round, k0_round, k_round[NST], v_round[NST], q_stored;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -98,7 +100,8 @@ __device__ __forceinline__ int kv_tiles_for(const FwdArgs& a, int q0) {
 
 __global__ void __launch_bounds__(fwd::NUM_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, const FwdArgs a) {
+                const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO,
+                const __grid_constant__ CUtensorMap mapQw, const FwdArgs a) {
     using namespace fwd;
     extern __shared__ __align__(1024) uint8_t smem[];
     // schedule trace (timeline_block < 0): {start ns, end ns, SM id, key tiles} of each of the first 1024 CTAs
@@ -172,6 +175,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             mbar_init(&sh.s_full[bf], 1);
             mbar_init(&sh.p_full[bf], 128);
             mbar_init(&sh.o_full[bf], 1);
+        }
+        mbar_init(&sh.q_round, 256);   // Q and the first K tile are rounded by the softmax warps, idle at that point
+        mbar_init(&sh.k0_round, 256);
+        mbar_init(&sh.q_stored, 1);
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(&sh.k_round[s], 64);
+            mbar_init(&sh.v_round[s], 64);
         }
         sh.abort_flag = 0;
         fence_mbar_init();
@@ -267,7 +277,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     if (nq >= total) return true;
                     const int s = jq % NST;
                     if (tq == 0 || jq >= n0) {  // first product that reads this key tile
-                        if (!wait(&sh.k_full[s], (jq / NST) & 1, W_KFULL, jq)) return false;
+                        // round_in_smem: the first key tile has a barrier of its own (other warps round it), so stage 0
+                        // of k_round starts counting at key tile NST
+                        uint64_t* kbar = !a.round_in_smem ? &sh.k_full[s] : (jq == 0 ? &sh.k0_round : &sh.k_round[s]);
+                        const uint32_t kpar = (a.round_in_smem && s == 0 && jq > 0) ? ((jq / NST) - 1) & 1 : (jq / NST) & 1;
+                        if (!wait(kbar, kpar, W_KFULL, jq)) return false;
                         tc_fence_after_sync();
                     }
                     issue_qk(tq, s, nq % 3);
@@ -276,14 +290,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     advance(jq, tq);
                     return true;
                 };
-                bool ok = wait(&sh.q_full, 0, W_QFULL, 0);
+                bool ok = wait(a.round_in_smem ? &sh.q_round : &sh.q_full, 0, W_QFULL, 0);
                 for (int i = 0; ok && i < 3; ++i) ok = next_qk();
                 int j = 0, t = (n0 > 0) ? 0 : 1;
                 for (int q = 0; ok && q < total; ++q) {
                     const int s = j % NST;
                     stamp(a, tlm, j, 0, 3 * t);
                     if (t == 0 || j >= n0) {
-                        if (!(ok = wait(&sh.v_full[s], (j / NST) & 1, W_VFULL, j))) break;
+                        if (!(ok = wait(a.round_in_smem ? &sh.v_round[s] : &sh.v_full[s], (j / NST) & 1, W_VFULL, j))) break;
                     }
                     if (!(ok = wait(&sh.p_full[q % 3], (q / 3) & 1, W_PFULL, j))) break;
                     stamp(a, tlm, j, 0, 1 + 3 * t);
@@ -295,6 +309,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                     advance(j, t);
                 }
             }
+        }
+        else if (a.round_in_smem && n > 0) {
+            // Warps 2 and 3 round what the TMA has landed to TF32 in place (add 0x1000, clear the low 13 bits: what
+            // the HBM pre-pass does, so every result is bit-identical to that path): every K and V tile of the ring
+            // but the first K tile, which the softmax warps take together with the two Q tiles while they have
+            // nothing else to do.  Short sequences only (the host decides): there the pre-pass costs
+            // more than this traffic on the shared-memory port that the S = Q K^T products are bound by.
+            const int rt = threadIdx.x - 64;  // 0..63
+            auto round_tile = [&](uint8_t* tile, int bytes) {
+                uint4* p4 = reinterpret_cast<uint4*>(tile);
+#pragma unroll 8
+                for (int i = rt; i < bytes / 16; i += 64) {
+                    uint4 x = p4[i];
+                    x.x = tf32_round_bits(x.x); x.y = tf32_round_bits(x.y);
+                    x.z = tf32_round_bits(x.z); x.w = tf32_round_bits(x.w);
+                    p4[i] = x;
+                }
+                fence_proxy_async_smem();
+            };
+            bool rok = true;
+            for (int j = 0; rok && j < n; ++j) {
+                const int s = j % NST;
+                const uint32_t par = (j / NST) & 1;
+                if (j > 0) {  // the softmax warps take Q and the first key tile
+                    if (!(rok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.k_full[s], par, W_KFULL, 2000 + j)))) break;
+                    round_tile(sK + s * TILE_BYTES, TILE_BYTES);
+                    mbar_arrive(&sh.k_round[s]);
+                }
+                if (!(rok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.v_full[s], par, W_VFULL, 2000 + j)))) break;
+                round_tile(sV + s * TILE_BYTES, TILE_BYTES);
+                mbar_arrive(&sh.v_round[s]);
+                if (j == 0 && a.store_q) {
+                    // the rounded Q tiles also go to the workspace (the backward reads Q from there); every thread of
+                    // the softmax warps have fenced their parts of Q and arrived on q_round
+                    if (rt == 0) {
+                        bool all_in = mbar_wait(wc, &sh.q_round, 0, W_QFULL, 2);
+                        if (all_in) {
+                            for (int t = 0; t < 2; ++t) {
+                                if (q0 + t * TILE < a.Tq) {
+                                    tma_store_4d(&mapQw, sQ + t * TILE_BYTES, 0, q0 + t * TILE, h, b);
+                                    tma_store_4d(&mapQw, sQ + t * TILE_BYTES + BOX_BYTES, HALF_D, q0 + t * TILE, h, b);
+                                }
+                            }
+                            bulk_commit_group();
+                            bulk_wait_group_read_all();
+                        }
+                        mbar_arrive(&sh.q_stored);  // the epilogue may reuse the Q buffer
+                    }
+                    __syncwarp();
+                }
+            }
+            if (!rok && a.store_q && rt == 0) mbar_arrive(&sh.q_stored);
         }
         // teardown of the control warps (kept inside this branch: the two register regimes never
         // share code after the hand-over)
@@ -350,6 +416,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             tmem_wait_st();
         }
 
+        if (a.round_in_smem && n > 0) {
+            // Q (both tiles) and the first K tile: rounded by the 256 softmax threads, which wait for the first scores
+            // anyway (a tile without keys of its own still takes its share)
+            const int st = threadIdx.x - 128;  // 0..255
+            auto round_part = [&](uint8_t* buf, int bytes) {
+                uint4* p4 = reinterpret_cast<uint4*>(buf);
+#pragma unroll 4
+                for (int i = st; i < bytes / 16; i += 256) {
+                    uint4 x = p4[i];
+                    x.x = tf32_round_bits(x.x); x.y = tf32_round_bits(x.y);
+                    x.z = tf32_round_bits(x.z); x.w = tf32_round_bits(x.w);
+                    p4[i] = x;
+                }
+                fence_proxy_async_smem();
+            };
+            if (__all_sync(0xffffffffu, mbar_wait(wc, &sh.q_full, 0, W_QFULL, 4))) {
+                round_part(sQ, 2 * TILE_BYTES);
+                mbar_arrive(&sh.q_round);
+                if (__all_sync(0xffffffffu, mbar_wait(wc, &sh.k_full[0], 0, W_KFULL, 4000))) {
+                    round_part(sK, TILE_BYTES);
+                    mbar_arrive(&sh.k0_round);
+                }
+            }
+        }
         int q_prev = 0;  // number of this tile's previous product
         for (int j = 0; j < nt; ++j) {
             stamp(a, tls, j, 1 + t, 0);
@@ -498,6 +588,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         // Rows past the end of the sequence are clipped by the copy.
         // (a tile that had no key tile to wait for must still let the load of its Q land before reusing the buffer)
         if (nt == 0 && n > 0) __all_sync(0xffffffffu, mbar_wait(wc, &sh.q_full, 0, W_QFULL, 0));
+        // ... and the store of the rounded Q tiles must have read it
+        if (a.round_in_smem && a.store_q && n > 0) __all_sync(0xffffffffu, mbar_wait(wc, &sh.q_stored, 0, W_QFULL, 3));
         {
             uint8_t* srow = sQ + t * TILE_BYTES + row * 128;
 #pragma unroll
@@ -534,7 +626,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 }
 
 int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
-                    const FwdArgs& a, cudaStream_t stream) {
+                    const CUtensorMap& mqw, const FwdArgs& a, cudaStream_t stream) {
     // the opt-in to large dynamic shared memory is per device: once per device, safe from any number of host threads
     static std::once_flag attr_once[HK_MAX_DEVICES];
     static cudaError_t attr_rc[HK_MAX_DEVICES];
@@ -548,7 +640,7 @@ int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     const long long nblocks = (long long)a.n_qtiles * a.BH;
     if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
     timing_mark(TIMED_FWD, true, stream);
-    attn_fwd_kernel<<<(unsigned)nblocks, fwd::NUM_THREADS, fwd::SMEM_BYTES, stream>>>(mq, mk, mv, mo, a);
+    attn_fwd_kernel<<<(unsigned)nblocks, fwd::NUM_THREADS, fwd::SMEM_BYTES, stream>>>(mq, mk, mv, mo, mqw, a);
     timing_mark(TIMED_FWD, false, stream);
     count_launch();
     return check_launch();

@@ -58,6 +58,7 @@ extern "C" int hk_attn_forward_static_scratch(const hk_attn_fwd_params* p, void*
     hk_attn_fwd_params q = *p;  // the caller's block is left untouched
     q.workspace = nullptr;
     q.workspace_bytes = 0;
+    q.flags |= HK_FLAG_ROUND_IN_HBM;  // this entry point's contract is the pre-pass into the built-in scratch
     const size_t need = hk_attn_fwd_workspace_bytes(&q);
     if (need > kScratchBytes) return HK_ERR_STATIC_SCRATCH;
     if (need > 0) {

@@ -18,6 +18,8 @@ struct FwdArgs {
     int dropout_mode;  // 0 none, 1 dense mask, 2 Philox
     int drop_scaled;   // 1: inverted dropout (normaliser over all visible keys, kept terms times keep_scale)
     int continue_state;  // 1: O, LSE hold the result over earlier keys and are the starting state
+    int round_in_smem;   // 1: Q, K, V arrive unrounded and are rounded to TF32 in shared memory after the TMA landing
+    int store_q;         // with round_in_smem: the rounded Q tiles are also written out (map mqw), for the backward
     float keep_scale;  // 1/(1-p) when drop_scaled, else 1
     uint32_t drop_thr;
     uint32_t bh_pos0;  // added to the local (batch, head) index in the Philox counter
@@ -29,6 +31,7 @@ struct FwdArgs {
 
 // mq, mk, mv: TMA maps of the (rounded) operands; mo: map of O, the destination of the kernel's bulk stores.
 int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                    const CUtensorMap& mqw,
                     const FwdArgs& a, cudaStream_t stream);
 
 struct BwdArgs {
@@ -47,6 +50,7 @@ struct BwdArgs {
     float scale, scale_log2e;
     int causal;
     int accum_dkdv;
+    int round_kv;      // 1: K and V arrive unrounded; the compute warps round them to TF32 once they have landed
     int dropout_mode;
     int drop_scaled;   // 1: inverted dropout; p below is then the softmax over all visible keys
     float dp_scale;    // factor of dP inside dS: scale, times 1/(1-p) when drop_scaled

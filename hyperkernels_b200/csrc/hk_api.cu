@@ -204,9 +204,21 @@ int hk_attn_dropout_mask_slices(float* mask, uint32_t bh_pos0, int BH, int64_t T
     return HK_OK;
 }
 
+// Where the operands are rounded to TF32.  For short sequences the kernels do it in shared memory after the TMA has
+// landed a tile (forward: Q, K, V; backward: K, V), for long ones an HBM pre-pass writes rounded copies into the
+// workspace: the pre-pass costs two passes over every tensor, the in-kernel rounding costs shared-memory bandwidth
+// once per tile LOAD, and a K/V tile is loaded once per 256 query rows (and what the pre-pass reads from HBM the
+// kernel then reads itself, cold).  Measured on a B200: forward kernel +2.3 us at
+// B8 H12 T1024 causal (against 18 us of pre-pass for K and V), +16 % at T16384.  Both give the same bits.
+static bool round_in_kernel(uint32_t flags, int64_t Tq, bool causal) {
+    if (flags & (HK_FLAG_OPERANDS_PREROUNDED | HK_FLAG_ROUND_IN_HBM)) return false;
+    return Tq >= 512 && Tq * (causal ? 1 : 2) <= 2048;  // below 512 rows a CTA has one or two steps and nothing to hide it under
+}
+
 size_t hk_attn_fwd_workspace_bytes(const hk_attn_fwd_params* p) {
     if (!p || (p->flags & HK_FLAG_OPERANDS_PREROUNDED)) return 0;
     if (p->B <= 0 || p->nh <= 0 || p->T <= 0) return 0;
+    if (round_in_kernel(p->flags, p->T, p->is_causal != 0)) return 0;  // rounded in shared memory: nothing is required
     const int64_t Tk = p->kv_len > 0 ? p->kv_len : p->T;
     const size_t bh = (size_t)p->B * p->nh;
     return align_up(bh * p->T * 256, 256) + 2 * align_up(bh * Tk * 256, 256);
@@ -272,11 +284,23 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     if (rc != HK_OK) return rc;
 
     const int B = p->B, H = p->nh, BH = B * H;
-    CUtensorMap mq, mk, mv;
-    if (p->flags & HK_FLAG_OPERANDS_PREROUNDED) {
+    CUtensorMap mq, mk, mv, mqw;
+    const bool in_kernel = round_in_kernel(p->flags, Tq, p->is_causal != 0);
+    float* q_rounded_out = nullptr;
+    if ((p->flags & HK_FLAG_OPERANDS_PREROUNDED) || in_kernel) {
+        // the kernel reads the caller's tensors: already rounded, or rounded in shared memory after the TMA landing
         if ((rc = make_tile_map(&mq, p->Q, HEAD_DIM, B, H, Tq, p->q_strideB, p->q_strideM, p->q_strideH, TILE))) return rc;
         if ((rc = make_tile_map(&mk, p->K, HEAD_DIM, B, H, Tk, p->k_strideB, p->k_strideM, p->k_strideH, TILE))) return rc;
         if ((rc = make_tile_map(&mv, p->V, HEAD_DIM, B, H, Tk, p->v_strideB, p->v_strideM, p->v_strideH, TILE, true))) return rc;
+        // a workspace, if the caller gave one, receives the rounded Q where the pre-pass would have put it
+        // (HK_FLAG_REUSE_FWD_ROUNDED in the backward)
+        if (in_kernel && p->workspace && p->workspace_bytes >= align_up((size_t)BH * Tq * 256, 256) &&
+            !(reinterpret_cast<uintptr_t>(p->workspace) & 255u))
+            q_rounded_out = static_cast<float*>(p->workspace);
+        mqw = mq;
+        if (q_rounded_out &&
+            (rc = make_tile_map(&mqw, q_rounded_out, HEAD_DIM, B, H, Tq, (int64_t)H * Tq * 64, 64, Tq * 64, TILE)))
+            return rc;
     } else {
         const size_t need = hk_attn_fwd_workspace_bytes(p);
         if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u))
@@ -296,6 +320,7 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
         if ((rc = make_tile_map(&mq, qr, HEAD_DIM, B, H, Tq, (int64_t)H * Tq * 64, 64, Tq * 64, TILE))) return rc;
         if ((rc = make_tile_map(&mk, kr, HEAD_DIM, B, H, Tk, (int64_t)H * Tk * 64, 64, Tk * 64, TILE))) return rc;
         if ((rc = make_tile_map(&mv, vr, HEAD_DIM, B, H, Tk, (int64_t)H * Tk * 64, 64, Tk * 64, TILE, true))) return rc;
+        mqw = mq;
     }
 
     FwdArgs a{};
@@ -312,6 +337,8 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     a.keep_scale = keep_scale_of(p->dropout_p, mode, p->flags);
     a.drop_scaled = (mode != 0 && (p->flags & HK_FLAG_DROPOUT_SCALED)) ? 1 : 0;
     a.continue_state = (p->flags & HK_FLAG_CONTINUE_SOFTMAX_STATE) ? 1 : 0;
+    a.round_in_smem = in_kernel ? 1 : 0;
+    a.store_q = q_rounded_out ? 1 : 0;
     if (a.continue_state && a.drop_scaled) return HK_ERR_UNSUPPORTED;
     a.drop_thr = hk_philox_threshold(p->dropout_p);
     a.seed = p->dropout_seed; a.offset = p->dropout_offset; a.bh_pos0 = p->bh_pos0;
@@ -321,7 +348,7 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     a.timeline_block = g_timeline_block.load();
     CUtensorMap mo;
     if ((rc = make_tile_map(&mo, p->O, HEAD_DIM, B, H, Tq, p->o_strideB, p->o_strideM, p->o_strideH, TILE))) return rc;
-    return launch_attn_fwd(mq, mk, mv, mo, a, stream);
+    return launch_attn_fwd(mq, mk, mv, mo, mqw, a, stream);
 }
 
 int hk_attn_bwd_precompute_D(const hk_attn_bwd_params* p, void* stream_) {
@@ -412,6 +439,7 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     float* dO_rounded = nullptr;
     // the tensors the MMAs read: the caller's (pre-rounded) or the rounded copies in the workspace
     View4 tQ = vQ, tK = vK, tV = vV, tdO = vdO;
+    bool round_kv = false;
     if (!(p->flags & HK_FLAG_OPERANDS_PREROUNDED)) {
         const size_t need = hk_attn_bwd_workspace_bytes(p);
         if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u))
@@ -424,25 +452,32 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
         float* vr = reinterpret_cast<float*>(ws + qb + kb);
         dO_rounded = reinterpret_cast<float*>(ws + qb + 2 * kb);
         const bool reuse = (p->flags & HK_FLAG_REUSE_FWD_ROUNDED) != 0;
+        round_kv = round_in_kernel(p->flags, Tq, p->is_causal != 0);
         RoundJob job{};
         job.H = H; job.BH = BH;
         int n = 0;
         if (!reuse) {
-            job.src[0] = vQ; job.src[1] = vK; job.src[2] = vV;
-            job.dst[0] = qr; job.dst[1] = kr; job.dst[2] = vr;
-            job.T[0] = (int)Tq; job.T[1] = (int)Tk; job.T[2] = (int)Tk;
-            n = 3;
+            job.src[n] = vQ; job.dst[n] = qr; job.T[n] = (int)Tq;
+            ++n;
+            if (!round_kv) {
+                job.src[n] = vK; job.dst[n] = kr; job.T[n] = (int)Tk;
+                ++n;
+                job.src[n] = vV; job.dst[n] = vr; job.T[n] = (int)Tk;
+                ++n;
+            }
         }
         if (d_given) {  // otherwise the D pre-pass writes the rounded dO while it reads dO
             job.src[n] = vdO; job.dst[n] = dO_rounded; job.T[n] = (int)Tq;
             ++n;
         }
         job.n = n;
-        if ((rc = launch_round_tf32(job, stream))) return rc;
+        if (n > 0 && (rc = launch_round_tf32(job, stream))) return rc;
         tQ = View4{qr, (int64_t)H * Tq * 64, 64, Tq * 64};
         tdO = View4{dO_rounded, (int64_t)H * Tq * 64, 64, Tq * 64};
-        tK = View4{kr, (int64_t)H * Tk * 64, 64, Tk * 64};
-        tV = View4{vr, (int64_t)H * Tk * 64, 64, Tk * 64};
+        if (!round_kv) {  // otherwise the kernel reads the caller's K and V and rounds them in shared memory
+            tK = View4{kr, (int64_t)H * Tk * 64, 64, Tk * 64};
+            tV = View4{vr, (int64_t)H * Tk * 64, 64, Tk * 64};
+        }
     }
     if ((rc = make_tile_map(&m.q, tQ.ptr, HEAD_DIM, B, H, Tq, tQ.sB, tQ.sM, tQ.sH, TILE, false))) return rc;
     if ((rc = make_tile_map(&m.k, tK.ptr, HEAD_DIM, B, H, Tk, tK.sB, tK.sM, tK.sH, TILE, false))) return rc;
@@ -484,6 +519,7 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     a.scale = p->scale; a.scale_log2e = p->scale * LOG2E;
     a.causal = p->is_causal ? 1 : 0;
     a.accum_dkdv = (p->flags & HK_FLAG_ACCUM_DKDV) ? 1 : 0;
+    a.round_kv = round_kv ? 1 : 0;
     a.dropout_mode = mode;
     a.drop_scaled = (mode != 0 && (p->flags & HK_FLAG_DROPOUT_SCALED)) ? 1 : 0;
     a.dv_scale = keep_scale_of(p->dropout_p, mode, p->flags);

@@ -64,7 +64,7 @@ enum {
      * with Philox4x32-10; see hk_attn_dropout_mask for the host twin. */
     HK_FLAG_PHILOX_DROPOUT = 1u << 0,
     /* Q, K, V (and dO) already hold TF32-representable values (low 13 mantissa
-     * bits zero): skip the operand-rounding pre-pass and its workspace. */
+     * bits zero): skip the operand rounding and its workspace. */
     HK_FLAG_OPERANDS_PREROUNDED = 1u << 1,
     /* backward: add into dK/dV instead of overwriting them (a K/V block that
      * travels round a sequence-sharded ring carries its gradients with it). */
@@ -75,7 +75,8 @@ enum {
      * kernel taken alone); otherwise hk_attn_backward computes it from dO and O. */
     HK_FLAG_D_PRECOMPUTED = 1u << 4,
     /* backward: `workspace` is the one hk_attn_forward was given for these same Q, K, V
-     * (same shapes) and still holds their rounded copies: do not round them again. */
+     * (same shapes, same is_causal, same rounding flags) and still holds what that call left
+     * there: do not round again what it holds. */
     HK_FLAG_REUSE_FWD_ROUNDED = 1u << 5,
     /* forward and backward: inverted dropout instead of the reference's drop-then-renormalise
      * (no reference counterpart).  The softmax is normalised over ALL visible keys, the kept
@@ -88,7 +89,13 @@ enum {
      * LSE -- the previous result acts as one more "key" of weight exp(LSE) and value O.  A caller that shards the
      * key sequence (a KV ring) chains its calls this way instead of merging partial results afterwards.  Not
      * available together with HK_FLAG_DROPOUT_SCALED.  No counterpart in the reference. */
-    HK_FLAG_CONTINUE_SOFTMAX_STATE = 1u << 7
+    HK_FLAG_CONTINUE_SOFTMAX_STATE = 1u << 7,
+    /* forward and backward: always round the operands with the HBM pre-pass into the workspace.  By default
+     * problems of 512 <= T <= 2048 (causal) or <= 1024 (otherwise) are rounded in shared memory after the TMA has
+     * landed a tile -- forward: Q, K, V, and no workspace is needed (one that is given receives the rounded Q
+     * for the backward); backward: K and V (Q and dO still come rounded from the workspace) -- because there
+     * the pre-pass costs more than the extra shared-memory traffic; both ways give the same bits. */
+    HK_FLAG_ROUND_IN_HBM = 1u << 8
 };
 
 /* ---- forward ------------------------------------------------------------

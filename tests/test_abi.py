@@ -71,8 +71,10 @@ def test_forward_argument_validation():
     assert L.hk_attn_forward(C.byref(p), None) == -4          # p outside [0,1)
     p = _fwd_block(); p.dropout_p = 0.1; p.dropout_mask = 0x1000; p.flags |= hk.FLAG_PHILOX_DROPOUT
     assert L.hk_attn_forward(C.byref(p), None) == -4          # both mask sources
-    p = _fwd_block(); p.flags = 0
-    assert L.hk_attn_forward(C.byref(p), None) == -5          # workspace missing
+    p = _fwd_block(); p.flags = hk.FLAG_ROUND_IN_HBM
+    assert L.hk_attn_forward(C.byref(p), None) == -5          # workspace missing (the HBM pre-pass needs one)
+    p = _fwd_block(); p.flags = 0; p.T = 4096
+    assert L.hk_attn_forward(C.byref(p), None) == -5          # long sequences are always rounded by the pre-pass
     p = _fwd_block(); p.dropout_p = 0.1; p.flags |= hk.FLAG_PHILOX_DROPOUT; p.k_pos0 = 2
     assert L.hk_attn_forward(C.byref(p), None) == -6          # unsupported Philox alignment
 
@@ -121,12 +123,20 @@ def test_broadcast_strides_are_refused():
 
 
 def test_workspace_sizes():
-    p = _fwd_block(); p.flags = 0; p.B, p.nh, p.T = 2, 3, 100
+    p = _fwd_block(); p.flags = hk.FLAG_ROUND_IN_HBM; p.B, p.nh, p.T = 2, 3, 100
     assert hk.fwd_workspace_bytes(p) == 3 * 2 * 3 * 100 * 256
     p.kv_len = 40
     assert hk.fwd_workspace_bytes(p) == 2 * 3 * 256 * (100 + 2 * 40)
     p.flags = hk.FLAG_OPERANDS_PREROUNDED
     assert hk.fwd_workspace_bytes(p) == 0
+    # short sequences are rounded in shared memory: the forward needs no scratch at all
+    p.flags = 0; p.kv_len = 0
+    for T, causal, inside in ((100, False, False), (511, True, False), (512, False, True), (1024, False, True),
+                              (1025, False, False), (2048, True, True), (2049, True, False)):
+        p.T, p.is_causal = T, causal
+        assert (hk.fwd_workspace_bytes(p) == 0) == inside, (T, causal)
+        if not inside:
+            assert hk.fwd_workspace_bytes(p) == 3 * 2 * 3 * T * 256
     b = BP(); b.B, b.nh, b.T = 2, 3, 100
     assert hk.bwd_workspace_bytes(b) == 4 * 2 * 3 * 100 * 256
 

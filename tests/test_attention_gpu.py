@@ -539,13 +539,44 @@ def test_batch_head_slices_reproduce_the_whole_call_under_dropout():
     ok_status()
 
 
+@pytest.mark.parametrize("causal", [0, 1])
+@pytest.mark.parametrize("B,H,T", [(2, 3, 640), (1, 2, 556), (1, 1, 1024)])
+def test_rounding_in_shared_memory_equals_the_hbm_prepass(B, H, T, causal):
+    """Short sequences have their operands rounded to TF32 in shared memory after the TMA landing (forward: Q, K, V;
+    backward: K, V), long ones -- and every call with HK_FLAG_ROUND_IN_HBM -- by the HBM pre-pass into the workspace.
+    Same rounding function, same kernels: O, LSE, dK, dV must be identical bit for bit, dQ up to the order of its
+    atomic additions.  Also with the workspace handed from the forward to the backward (the forward leaves the rounded
+    Q there; HK_FLAG_REUSE_FWD_ROUNDED)."""
+    Q, K, V, dO = (dev(normal((B, H, T, 64), 900 + s)) for s in range(4))
+    O_h, L_h = hk.attention_forward(Q, K, V, SCALE, causal, round_in_hbm=True)
+    O_s, L_s = hk.attention_forward(Q, K, V, SCALE, causal)
+    ok_status()
+    assert torch.equal(O_h, O_s) and torch.equal(L_h, L_s)
+    g_h = hk.attention_backward(Q, K, V, O_h, dO, L_h, SCALE, causal, round_in_hbm=True)
+    g_s = hk.attention_backward(Q, K, V, O_h, dO, L_h, SCALE, causal)
+    ok_status()
+    assert torch.equal(g_h[1], g_s[1]) and torch.equal(g_h[2], g_s[2]) and torch.equal(g_h[3], g_s[3])
+    assert float((g_h[0] - g_s[0]).abs().max()) <= 1e-4
+    # forward and backward sharing one workspace
+    p = hk.MemEfficientBwdParams()
+    p.B, p.nh, p.T = B, H, T
+    ws = torch.empty(hk.bwd_workspace_bytes(p) + 256, dtype=torch.uint8, device="cuda")
+    ws.fill_(0x7F)  # nothing may be taken from a workspace the forward has not written
+    O_w, L_w = hk.attention_forward(Q, K, V, SCALE, causal, workspace=ws)
+    g_w = hk.attention_backward(Q, K, V, O_w, dO, L_w, SCALE, causal, workspace=ws, reuse_fwd_rounded=True)
+    ok_status()
+    assert torch.equal(O_w, O_h) and torch.equal(L_w, L_h)
+    assert torch.equal(g_w[1], g_h[1]) and torch.equal(g_w[2], g_h[2]) and torch.equal(g_w[3], g_h[3])
+    assert float((g_w[0] - g_h[0]).abs().max()) <= 1e-4
+
+
 def test_graphed_step_replays_the_direct_calls():
     """GraphedAttentionStep (forward + backward captured in a CUDA graph): a replay gives what the direct calls give,
     also after the inputs were refilled in place."""
     B, H, T = 2, 3, 320
     tQ, tK, tV, tdO = (dev(normal((B, H, T, 64), 90 + s)) for s in range(4))
     gs = hk.GraphedAttentionStep(tQ, tK, tV, tdO, SCALE, True)
-    assert gs.launches_per_replay == 4
+    assert gs.launches_per_replay == 4  # rounding pre-pass, forward, D pre-pass, backward (T < 512: rounded in HBM)
     for seed in (0, 1):
         if seed:
             for t_, s in zip((tQ, tK, tV, tdO), range(4)):
