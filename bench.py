@@ -343,7 +343,8 @@ def run_ours(args, cfg, rank, local_rank, world):
     samples = timed_samples(gstep.replay, args.steps * inner, flush, stream, torch)
     barrier()
     t_wall = time.perf_counter() - t_wall
-    launches = gstep.launches_per_replay * args.steps * inner
+    launches_per_step = int(gstep.launches_per_replay)
+    launches = launches_per_step * args.steps * inner
     ms, ms_mean = _median(samples), sum(samples) / len(samples)
     assert hk.last_device_status() == 0, "a bounded wait inside a kernel gave up"
 
@@ -439,7 +440,7 @@ def run_ours(args, cfg, rank, local_rank, world):
                        "config_id": args.config,
                        "l2": "256 MiB buffer written before every timed sample (untimed)",
                        "step": "hk_attn_forward + hk_attn_backward with every launch they make (operand rounding to TF32: in shared memory inside the kernels for 512 <= N <= 2048 causal / 1024 otherwise, else one HBM pre-pass per step; D pre-pass with dO rounding and dQ zeroing; the two main kernels), captured in a CUDA graph and replayed",
-                       "launches_per_step": int(gstep.launches_per_replay),
+                       "launches_per_step": launches_per_step,
                        "timing": f"median of {len(samples)} samples ({args.steps} steps x {inner} replays), one CUDA-event pair per replay",
                        "partition": "batch x head across GPUs, no collective"},
             "ms_per_step_mean": ms_mean,
