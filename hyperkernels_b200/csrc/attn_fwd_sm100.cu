@@ -101,7 +101,8 @@ __device__ __forceinline__ int kv_tiles_for(const FwdArgs& a, int q0) {
 __global__ void __launch_bounds__(fwd::NUM_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO,
-                const __grid_constant__ CUtensorMap mapQw, const FwdArgs a) {
+                const __grid_constant__ CUtensorMap mapQw, const __grid_constant__ CUtensorMap mapKw,
+                const __grid_constant__ CUtensorMap mapVw, const FwdArgs a) {
     using namespace fwd;
     extern __shared__ __align__(1024) uint8_t smem[];
     // schedule trace (timeline_block < 0): {start ns, end ns, SM id, key tiles} of each of the first 1024 CTAs
@@ -165,8 +166,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
     if (threadIdx.x == 64) {  // an idle warp takes the rest of the barriers
         for (int s = 0; s < NST; ++s) {
-            mbar_init(&sh.k_empty[s], 1);
-            mbar_init(&sh.v_empty[s], 1);
+            // round_in_smem: a stage is free when the MMAs have read it AND the rounding warps are done with it (they
+            // may still have a store of the rounded tile reading it)
+            mbar_init(&sh.k_empty[s], a.round_in_smem ? 2 : 1);
+            mbar_init(&sh.v_empty[s], a.round_in_smem ? 2 : 1);
         }
         // The score barriers belong to the score BUFFER, not to the tile: the warps of a tile may be a whole step
         // apart (the scores of the next step are there before the slowest warp has finished this one), and a
@@ -328,10 +331,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 }
                 fence_proxy_async_smem();
             };
+            // Each key/value tile is written out by the first query block that loads it: block qb takes the tiles
+            // from where block qb - 1 stops (under the causal mask later blocks see more keys, never fewer).
+            int j_store0 = 0;
+            if (a.store_q && qb > 0) {
+                const int qp = (qb - 1) * 2 * TILE;
+                j_store0 = max(kv_tiles_for(a, qp), kv_tiles_for(a, qp + TILE));
+            }
             bool rok = true;
             for (int j = 0; rok && j < n; ++j) {
                 const int s = j % NST;
                 const uint32_t par = (j / NST) & 1;
+                const bool store = a.store_q && j >= j_store0;
                 if (j > 0) {  // the softmax warps take Q and the first key tile
                     if (!(rok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.k_full[s], par, W_KFULL, 2000 + j)))) break;
                     round_tile(sK + s * TILE_BYTES, TILE_BYTES);
@@ -340,27 +351,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 if (!(rok = __all_sync(0xffffffffu, mbar_wait(wc, &sh.v_full[s], par, W_VFULL, 2000 + j)))) break;
                 round_tile(sV + s * TILE_BYTES, TILE_BYTES);
                 mbar_arrive(&sh.v_round[s]);
-                if (j == 0 && a.store_q) {
-                    // the rounded Q tiles also go to the workspace (the backward reads Q from there); every thread of
-                    // the softmax warps have fenced their parts of Q and arrived on q_round
-                    if (rt == 0) {
-                        bool all_in = mbar_wait(wc, &sh.q_round, 0, W_QFULL, 2);
-                        if (all_in) {
-                            for (int t = 0; t < 2; ++t) {
-                                if (q0 + t * TILE < a.Tq) {
-                                    tma_store_4d(&mapQw, sQ + t * TILE_BYTES, 0, q0 + t * TILE, h, b);
-                                    tma_store_4d(&mapQw, sQ + t * TILE_BYTES + BOX_BYTES, HALF_D, q0 + t * TILE, h, b);
+                if (rt == 0) {
+                    // one thread writes the rounded tiles out and hands the stages back.  It has arrived on the
+                    // tiles' barriers itself and waits for them: every thread's part is rounded and fenced.
+                    bool all_in = true;
+                    if (store || (j == 0 && a.store_q)) {
+                        if (j == 0 && a.store_q) {
+                            all_in = mbar_wait(wc, &sh.q_round, 0, W_QFULL, 2);
+                            if (all_in) {
+                                for (int t = 0; t < 2; ++t) {
+                                    if (q0 + t * TILE < a.Tq) {
+                                        tma_store_4d(&mapQw, sQ + t * TILE_BYTES, 0, q0 + t * TILE, h, b);
+                                        tma_store_4d(&mapQw, sQ + t * TILE_BYTES + BOX_BYTES, HALF_D, q0 + t * TILE, h, b);
+                                    }
                                 }
                             }
-                            bulk_commit_group();
-                            bulk_wait_group_read_all();
                         }
-                        mbar_arrive(&sh.q_stored);  // the epilogue may reuse the Q buffer
+                        if (store && all_in)
+                            all_in = mbar_wait(wc, j == 0 ? &sh.k0_round : &sh.k_round[s],
+                                               (s == 0 && j > 0) ? ((j / NST) - 1) & 1 : par, W_KFULL, 3000 + j) &&
+                                     mbar_wait(wc, &sh.v_round[s], par, W_VFULL, 3000 + j);
+                        if (store && all_in) {
+                            tma_store_4d(&mapKw, sK + s * TILE_BYTES, 0, j * TILE, h, b);
+                            tma_store_4d(&mapKw, sK + s * TILE_BYTES + BOX_BYTES, HALF_D, j * TILE, h, b);
+                            tma_store_4d(&mapVw, sV + s * TILE_BYTES, 0, j * TILE, h, b);
+                            tma_store_4d(&mapVw, sV + s * TILE_BYTES + BOX_BYTES, HALF_D, j * TILE, h, b);
+                        }
+                        bulk_commit_group();
+                        bulk_wait_group_read_all();
+                        if (j == 0 && a.store_q) mbar_arrive(&sh.q_stored);  // the epilogue may reuse the Q buffer
                     }
-                    __syncwarp();
+                    mbar_arrive(&sh.k_empty[s]);
+                    mbar_arrive(&sh.v_empty[s]);
                 }
+                __syncwarp();
             }
-            if (!rok && a.store_q && rt == 0) mbar_arrive(&sh.q_stored);
+            if (!rok && a.store_q && rt == 0) mbar_arrive(&sh.q_stored);  // (a second arrival is harmless)
         }
         // teardown of the control warps (kept inside this branch: the two register regimes never
         // share code after the hand-over)
@@ -626,7 +652,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 }
 
 int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
-                    const CUtensorMap& mqw, const FwdArgs& a, cudaStream_t stream) {
+                    const CUtensorMap& mqw, const CUtensorMap& mkw, const CUtensorMap& mvw, const FwdArgs& a,
+                    cudaStream_t stream) {
     // the opt-in to large dynamic shared memory is per device: once per device, safe from any number of host threads
     static std::once_flag attr_once[HK_MAX_DEVICES];
     static cudaError_t attr_rc[HK_MAX_DEVICES];
@@ -640,7 +667,7 @@ int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     const long long nblocks = (long long)a.n_qtiles * a.BH;
     if (nblocks <= 0 || nblocks > 0x7fffffffLL) return HK_ERR_BAD_SHAPE;
     timing_mark(TIMED_FWD, true, stream);
-    attn_fwd_kernel<<<(unsigned)nblocks, fwd::NUM_THREADS, fwd::SMEM_BYTES, stream>>>(mq, mk, mv, mo, mqw, a);
+    attn_fwd_kernel<<<(unsigned)nblocks, fwd::NUM_THREADS, fwd::SMEM_BYTES, stream>>>(mq, mk, mv, mo, mqw, mkw, mvw, a);
     timing_mark(TIMED_FWD, false, stream);
     count_launch();
     return check_launch();

@@ -19,7 +19,8 @@ struct FwdArgs {
     int drop_scaled;   // 1: inverted dropout (normaliser over all visible keys, kept terms times keep_scale)
     int continue_state;  // 1: O, LSE hold the result over earlier keys and are the starting state
     int round_in_smem;   // 1: Q, K, V arrive unrounded and are rounded to TF32 in shared memory after the TMA landing
-    int store_q;         // with round_in_smem: the rounded Q tiles are also written out (map mqw), for the backward
+    int store_q;         // with round_in_smem: the rounded Q, K and V tiles are also written out (maps mqw, mkw, mvw), where
+                         // the HBM pre-pass would have put them, for a backward call that reuses them
     float keep_scale;  // 1/(1-p) when drop_scaled, else 1
     uint32_t drop_thr;
     uint32_t bh_pos0;  // added to the local (batch, head) index in the Philox counter
@@ -31,7 +32,7 @@ struct FwdArgs {
 
 // mq, mk, mv: TMA maps of the (rounded) operands; mo: map of O, the destination of the kernel's bulk stores.
 int launch_attn_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
-                    const CUtensorMap& mqw,
+                    const CUtensorMap& mqw, const CUtensorMap& mkw, const CUtensorMap& mvw,
                     const FwdArgs& a, cudaStream_t stream);
 
 struct BwdArgs {

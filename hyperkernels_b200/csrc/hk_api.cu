@@ -284,7 +284,7 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     if (rc != HK_OK) return rc;
 
     const int B = p->B, H = p->nh, BH = B * H;
-    CUtensorMap mq, mk, mv, mqw;
+    CUtensorMap mq, mk, mv, mqw, mkw, mvw;
     const bool in_kernel = round_in_kernel(p->flags, Tq, p->is_causal != 0);
     float* q_rounded_out = nullptr;
     if ((p->flags & HK_FLAG_OPERANDS_PREROUNDED) || in_kernel) {
@@ -292,15 +292,21 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
         if ((rc = make_tile_map(&mq, p->Q, HEAD_DIM, B, H, Tq, p->q_strideB, p->q_strideM, p->q_strideH, TILE))) return rc;
         if ((rc = make_tile_map(&mk, p->K, HEAD_DIM, B, H, Tk, p->k_strideB, p->k_strideM, p->k_strideH, TILE))) return rc;
         if ((rc = make_tile_map(&mv, p->V, HEAD_DIM, B, H, Tk, p->v_strideB, p->v_strideM, p->v_strideH, TILE, true))) return rc;
-        // a workspace, if the caller gave one, receives the rounded Q where the pre-pass would have put it
+        // a workspace, if the caller gave one, receives the rounded Q, K, V where the pre-pass would have put them
         // (HK_FLAG_REUSE_FWD_ROUNDED in the backward)
-        if (in_kernel && p->workspace && p->workspace_bytes >= align_up((size_t)BH * Tq * 256, 256) &&
+        const size_t qb = align_up((size_t)BH * Tq * 256, 256), kb = align_up((size_t)BH * Tk * 256, 256);
+        if (in_kernel && p->workspace && p->workspace_bytes >= qb + 2 * kb &&
             !(reinterpret_cast<uintptr_t>(p->workspace) & 255u))
             q_rounded_out = static_cast<float*>(p->workspace);
-        mqw = mq;
-        if (q_rounded_out &&
-            (rc = make_tile_map(&mqw, q_rounded_out, HEAD_DIM, B, H, Tq, (int64_t)H * Tq * 64, 64, Tq * 64, TILE)))
-            return rc;
+        mqw = mq; mkw = mk; mvw = mv;
+        if (q_rounded_out) {
+            uint8_t* ws = static_cast<uint8_t*>(p->workspace);
+            float* kr = reinterpret_cast<float*>(ws + qb);
+            float* vr = reinterpret_cast<float*>(ws + qb + kb);
+            if ((rc = make_tile_map(&mqw, q_rounded_out, HEAD_DIM, B, H, Tq, (int64_t)H * Tq * 64, 64, Tq * 64, TILE))) return rc;
+            if ((rc = make_tile_map(&mkw, kr, HEAD_DIM, B, H, Tk, (int64_t)H * Tk * 64, 64, Tk * 64, TILE))) return rc;
+            if ((rc = make_tile_map(&mvw, vr, HEAD_DIM, B, H, Tk, (int64_t)H * Tk * 64, 64, Tk * 64, TILE, true))) return rc;
+        }
     } else {
         const size_t need = hk_attn_fwd_workspace_bytes(p);
         if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u))
@@ -320,7 +326,7 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
         if ((rc = make_tile_map(&mq, qr, HEAD_DIM, B, H, Tq, (int64_t)H * Tq * 64, 64, Tq * 64, TILE))) return rc;
         if ((rc = make_tile_map(&mk, kr, HEAD_DIM, B, H, Tk, (int64_t)H * Tk * 64, 64, Tk * 64, TILE))) return rc;
         if ((rc = make_tile_map(&mv, vr, HEAD_DIM, B, H, Tk, (int64_t)H * Tk * 64, 64, Tk * 64, TILE, true))) return rc;
-        mqw = mq;
+        mqw = mq; mkw = mk; mvw = mv;
     }
 
     FwdArgs a{};
@@ -348,7 +354,7 @@ int hk_attn_forward(const hk_attn_fwd_params* p, void* stream_) {
     a.timeline_block = g_timeline_block.load();
     CUtensorMap mo;
     if ((rc = make_tile_map(&mo, p->O, HEAD_DIM, B, H, Tq, p->o_strideB, p->o_strideM, p->o_strideH, TILE))) return rc;
-    return launch_attn_fwd(mq, mk, mv, mo, mqw, a, stream);
+    return launch_attn_fwd(mq, mk, mv, mo, mqw, mkw, mvw, a, stream);
 }
 
 int hk_attn_bwd_precompute_D(const hk_attn_bwd_params* p, void* stream_) {
@@ -452,7 +458,9 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
         float* vr = reinterpret_cast<float*>(ws + qb + kb);
         dO_rounded = reinterpret_cast<float*>(ws + qb + 2 * kb);
         const bool reuse = (p->flags & HK_FLAG_REUSE_FWD_ROUNDED) != 0;
-        round_kv = round_in_kernel(p->flags, Tq, p->is_causal != 0);
+        // a stand-alone backward of a short sequence rounds K and V in shared memory; one that reuses the forward's
+        // workspace finds them there (whichever way the forward rounded them)
+        round_kv = !reuse && round_in_kernel(p->flags, Tq, p->is_causal != 0);
         RoundJob job{};
         job.H = H; job.BH = BH;
         int n = 0;

@@ -92,9 +92,10 @@ enum {
     HK_FLAG_CONTINUE_SOFTMAX_STATE = 1u << 7,
     /* forward and backward: always round the operands with the HBM pre-pass into the workspace.  By default
      * problems of 512 <= T <= 2048 (causal) or <= 1024 (otherwise) are rounded in shared memory after the TMA has
-     * landed a tile -- forward: Q, K, V, and no workspace is needed (one that is given receives the rounded Q
-     * for the backward); backward: K and V (Q and dO still come rounded from the workspace) -- because there
-     * the pre-pass costs more than the extra shared-memory traffic; both ways give the same bits. */
+     * landed a tile -- forward: Q, K, V, and no workspace is needed (one that is given and large enough receives
+     * the rounded tensors for a backward with HK_FLAG_REUSE_FWD_ROUNDED); stand-alone backward: K and V (Q and dO
+     * are still rounded into the workspace) -- because there the pre-pass costs more than the extra
+     * shared-memory traffic; both ways give the same bits. */
     HK_FLAG_ROUND_IN_HBM = 1u << 8
 };
 
