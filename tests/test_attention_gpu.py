@@ -570,6 +570,28 @@ def test_rounding_in_shared_memory_equals_the_hbm_prepass(B, H, T, causal):
     assert float((g_w[0] - g_h[0]).abs().max()) <= 1e-4
 
 
+@pytest.mark.parametrize("Tq,Tk,q_pos0", [(640, 896, 256), (512, 1024, 0), (700, 300, 0)])
+def test_workspace_handed_from_forward_to_backward_with_unequal_lengths(Tq, Tk, q_pos0):
+    """The forward writes the rounded K/V tiles it loads into the workspace, each tile by the first query block that
+    loads it; key tiles no query sees are never written, and the backward must not read them.  Poisoned workspace,
+    causal mask with a query offset, more keys than any query sees, fewer keys than queries."""
+    B, H = 1, 2
+    Q, dO = dev(normal((B, H, Tq, 64), 910)), dev(normal((B, H, Tq, 64), 911))
+    K, V = dev(normal((B, H, Tk, 64), 912)), dev(normal((B, H, Tk, 64), 913))
+    O_h, L_h = hk.attention_forward(Q, K, V, SCALE, True, q_pos0=q_pos0, round_in_hbm=True)
+    g_h = hk.attention_backward(Q, K, V, O_h, dO, L_h, SCALE, True, q_pos0=q_pos0, round_in_hbm=True)
+    p = hk.MemEfficientBwdParams()
+    p.B, p.nh, p.T, p.kv_len = B, H, Tq, Tk
+    ws = torch.empty(hk.bwd_workspace_bytes(p) + 256, dtype=torch.uint8, device="cuda")
+    ws.fill_(0x7F)
+    O_w, L_w = hk.attention_forward(Q, K, V, SCALE, True, q_pos0=q_pos0, workspace=ws)
+    g_w = hk.attention_backward(Q, K, V, O_w, dO, L_w, SCALE, True, q_pos0=q_pos0, workspace=ws, reuse_fwd_rounded=True)
+    ok_status()
+    assert torch.equal(O_w, O_h) and torch.equal(L_w, L_h)
+    assert torch.equal(g_w[1], g_h[1]) and torch.equal(g_w[2], g_h[2])
+    assert float((g_w[0] - g_h[0]).abs().max()) <= 1e-4
+
+
 def test_graphed_step_replays_the_direct_calls():
     """GraphedAttentionStep (forward + backward captured in a CUDA graph): a replay gives what the direct calls give,
     also after the inputs were refilled in place."""
