@@ -12,6 +12,9 @@ copy directions use different DMA engines and the link is full duplex).  The
 chunks are runs of consecutive (batch, head) slices, so a single-batch problem
 with many heads is pipelined too; small problems (under 2 MB per tensor and
 chunk) are not cut, the extra launches would cost more than the overlap gains.
+The whole step -- every copy, every launch, the dependencies between the three
+queues -- is captured in a CUDA graph the second time it is called with the same
+host tensors and replayed from then on, so the host issues one call per step.
 
 Everything on the device goes through the C ABI (``hk_attn_forward`` and
 ``hk_attn_backward`` per chunk, with preallocated buffers and workspace); torch
@@ -36,14 +39,14 @@ class HostAttentionStep:
     """
 
     def __init__(self, B: int, H: int, T: int, scale: float, causal: bool, *, chunks: Optional[int] = None,
-                 device=None, dropout_p: float = 0.0, philox_seed: Optional[int] = None, philox_offset: int = 0):
+                 n_slots: int = 3, graph: bool = True, device=None, dropout_p: float = 0.0, philox_seed: Optional[int] = None, philox_offset: int = 0):
         import torch
 
         self.torch = torch
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         n = B * H  # independent slices; a chunk is a run of them, handed to the kernels as a batch of one-head items
         if chunks is None:
-            chunks = next(c for c in (4, 2, 1) if n % c == 0 and (c == 1 or n // c * T * 256 >= (2 << 20)))
+            chunks = next(c for c in (8, 4, 2, 1) if n % c == 0 and (c == 1 or n // c * T * 256 >= (2 << 20)))
         if n % chunks != 0:
             raise ValueError("batch x heads must divide into equal chunks")
         self.B, self.H, self.T, self.scale, self.causal = B, H, T, float(scale), bool(causal)
@@ -55,7 +58,7 @@ class HostAttentionStep:
             self.drop = dict(dropout_p=dropout_p, philox_seed=philox_seed)
         self.philox_offset = philox_offset
         shp, lshp = (self.cb, 1, T, 64), (self.cb, 1, T)
-        n_slots = min(2, chunks)
+        n_slots = max(1, min(n_slots, chunks))
         self.slots = []
         for _ in range(n_slots):
             s = {k: torch.empty(shp, dtype=torch.float32, device=self.device)
@@ -69,10 +72,40 @@ class HostAttentionStep:
         self.ev_in = [torch.cuda.Event() for _ in range(chunks)]
         self.ev_cmp = [torch.cuda.Event() for _ in range(chunks)]
         self.ev_out = [torch.cuda.Event() for _ in range(chunks)]
+        self.use_graph = bool(graph)
+        self._seen_key = None    # host tensors of the last eager step
+        self._graph_key = None   # host tensors the captured graph copies from / to
+        self._graph = None
         self.h2d_bytes = 4 * B * H * T * 64 * 4
         self.d2h_bytes = 4 * B * H * T * 64 * 4 + B * H * T * 4
 
     def step(self, hQ, hK, hV, hdO, hO, hLSE, hdQ, hdK, hdV) -> None:
+        torch = self.torch
+        args = (hQ, hK, hV, hdO, hO, hLSE, hdQ, hdK, hdV)
+        if not self.use_graph:
+            return self._enqueue(*args)
+        key = tuple(int(t.data_ptr()) for t in args)
+        if key == self._graph_key:
+            self._graph.replay()  # on the caller's current stream
+            return
+        if key != self._seen_key:
+            # first step with these tensors: issue it call by call (first-call set-up of the library happens here)
+            self._seen_key = key
+            return self._enqueue(*args)
+        # second step with the same tensors: capture it, then run the capture
+        cur = torch.cuda.current_stream(self.device)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(cur)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                self._enqueue(*args)
+        cur.wait_stream(side)
+        self._graph, self._graph_key = g, key
+        self._keep = args  # the graph holds raw pointers into these tensors
+        g.replay()
+
+    def _enqueue(self, hQ, hK, hV, hdO, hO, hLSE, hdQ, hdK, hdV) -> None:
         torch = self.torch
         n = self.B * self.H
         # [B, H, ...] contiguous == [B*H, 1, ...]

@@ -484,9 +484,12 @@ def test_host_step_pipeline_matches_direct_calls(chunks):
     hO, hdQ, hdK, hdV = (torch.full((B, H, T, 64), float("nan")).pin_memory() for _ in range(4))
     hLSE = torch.full((B, H, T), float("nan")).pin_memory()
     hs = hk.HostAttentionStep(B, H, T, SCALE, True, chunks=chunks)
-    for _ in range(2):  # the second step reuses every buffer slot
+    for it in range(3):  # first step issued call by call, second captured in a CUDA graph and replayed, third replayed
+        for t in (hO, hdQ, hdK, hdV, hLSE):
+            t.fill_(float("nan"))
         hs.step(*hin, hO, hLSE, hdQ, hdK, hdV)
         torch.cuda.synchronize()
+        assert torch.equal(hO, O.cpu()) and torch.equal(hdK, dK.cpu()), it
     ok_status()
     assert torch.equal(hO, O.cpu()) and torch.equal(hLSE, LSE.cpu())
     assert torch.equal(hdK, dK.cpu()) and torch.equal(hdV, dV.cpu())
