@@ -595,6 +595,43 @@ def test_workspace_handed_from_forward_to_backward_with_unequal_lengths(Tq, Tk, 
     assert float((g_w[0] - g_h[0]).abs().max()) <= 1e-4
 
 
+def test_random_shapes_the_two_rounding_paths_and_the_workspace_hand_over_agree():
+    """Seeded random shapes (ragged lengths, unequal query/key lengths, position offsets, Philox dropout) around the
+    window in which the operands are rounded in shared memory: that path, the HBM pre-pass and the forward-to-backward
+    workspace hand-over must give identical O, LSE, dK, dV (dQ up to the order of its atomic additions)."""
+    import random
+
+    rnd = random.Random(2024)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    same = lambda a, b: torch.equal(torch.nan_to_num(a, nan=0.0, neginf=-1e30), torch.nan_to_num(b, nan=0.0, neginf=-1e30))
+    for case in range(24):
+        B, H = rnd.choice([(1, 1), (1, 3), (2, 2), (3, 5)])
+        causal = rnd.random() < 0.6
+        Tq = rnd.choice([512, 513, 600, 700, 1000, 1024, 1100, 1536, 2047, 2048, 300])
+        Tk = rnd.choice([128, 257, 777, 1024, 1500]) if rnd.random() < 0.3 else Tq
+        kw = dict(q_pos0=rnd.choice([0, 0, 128, 616]) if causal else 0, k_pos0=rnd.choice([0, 0, 64, 128]) if causal else 0)
+        if rnd.random() < 0.3:
+            kw.update(dropout_p=0.2, philox_seed=rnd.randrange(1 << 30), philox_offset=8 * rnd.randrange(100))
+        Q, dO = (torch.randn((B, H, Tq, 64), generator=g, device="cuda") for _ in range(2))
+        K, V = (torch.randn((B, H, Tk, 64), generator=g, device="cuda") for _ in range(2))
+        O1, L1 = hk.attention_forward(Q, K, V, SCALE, causal, round_in_hbm=True, **kw)
+        O2, L2 = hk.attention_forward(Q, K, V, SCALE, causal, **kw)
+        p = hk.MemEfficientBwdParams()
+        p.B, p.nh, p.T, p.kv_len = B, H, Tq, (Tk if Tk != Tq else 0)
+        ws = torch.empty(hk.bwd_workspace_bytes(p) + 256, dtype=torch.uint8, device="cuda")
+        ws.fill_(0x7F)
+        O3, L3 = hk.attention_forward(Q, K, V, SCALE, causal, workspace=ws, **kw)
+        g1 = hk.attention_backward(Q, K, V, O1, dO, L1, SCALE, causal, round_in_hbm=True, **kw)
+        g2 = hk.attention_backward(Q, K, V, O1, dO, L1, SCALE, causal, **kw)
+        g3 = hk.attention_backward(Q, K, V, O3, dO, L3, SCALE, causal, workspace=ws, reuse_fwd_rounded=True, **kw)
+        ok_status()
+        what = (case, B, H, Tq, Tk, causal, kw)
+        assert same(O1, O2) and same(L1, L2) and same(O1, O3) and same(L1, L3), what
+        assert same(g1[1], g2[1]) and same(g1[2], g2[2]) and same(g1[1], g3[1]) and same(g1[2], g3[2]), what
+        assert float((g1[0] - g2[0]).abs().max()) <= 1e-3 and float((g1[0] - g3[0]).abs().max()) <= 1e-3, what
+        assert bool(torch.isfinite(O2).all()), what
+
+
 def test_graphed_step_replays_the_direct_calls():
     """GraphedAttentionStep (forward + backward captured in a CUDA graph): a replay gives what the direct calls give,
     also after the inputs were refilled in place."""
