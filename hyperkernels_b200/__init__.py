@@ -32,6 +32,7 @@ from .attention import (  # noqa: F401
     FLAG_DROPOUT_SCALED,
     FLAG_CONTINUE_SOFTMAX_STATE,
     FLAG_ROUND_IN_HBM,
+    FLAG_DETERMINISTIC_DQ,
 )
 from .graph_step import GraphedAttentionStep  # noqa: F401
 from .host_step import HostAttentionStep  # noqa: F401

@@ -40,6 +40,7 @@ FLAG_REUSE_FWD_ROUNDED = 1 << 5
 FLAG_DROPOUT_SCALED = 1 << 6  # inverted dropout (kept terms / (1 - p), normaliser over all keys)
 FLAG_CONTINUE_SOFTMAX_STATE = 1 << 7  # forward: O, LSE hold the result over earlier keys; fold this call's keys in
 FLAG_ROUND_IN_HBM = 1 << 8  # always round operands with the HBM pre-pass (default: in shared memory for short sequences)
+FLAG_DETERMINISTIC_DQ = 1 << 9  # backward: dQ through per-KV-tile slabs added in a fixed order (same bits on every run)
 
 _f32p = C.POINTER(C.c_float)
 
@@ -283,7 +284,8 @@ def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropo
                        philox_seed: Optional[int] = None, philox_offset: int = 0, q_pos0: int = 0, k_pos0: int = 0,
                        bh_pos0: int = 0, prerounded: bool = False, D=None, d_precomputed: bool = False, accum_dkdv: bool = False,
                        accum_dq: bool = False, reuse_fwd_rounded: bool = False, dropout_scaled: bool = False,
-                       round_in_hbm: bool = False, workspace=None, dQ=None, dK=None, dV=None, stream=None):
+                       round_in_hbm: bool = False, deterministic_dq: bool = False, workspace=None, dQ=None, dK=None, dV=None,
+                       stream=None):
     """dQ, dK, dV, D = fused attention backward (fp32 CUDA tensors, [B,H,T,64])."""
     import torch
 
@@ -329,6 +331,8 @@ def attention_backward(Q, K, V, O, dO, LSE, scale: float, causal: bool, *, dropo
         flags |= FLAG_REUSE_FWD_ROUNDED
     if round_in_hbm:
         flags |= FLAG_ROUND_IN_HBM
+    if deterministic_dq:
+        flags |= FLAG_DETERMINISTIC_DQ
     p.flags = flags
     ws = _workspace(bwd_workspace_bytes(p), Q, workspace)
     if ws is not None:

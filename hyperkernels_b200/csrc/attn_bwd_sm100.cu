@@ -441,8 +441,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             auto reduce_dq = [&](int j) -> bool {
                 if (!mbar_wait(wc, &sh.dq_staged, j & 1, W_DQSTAGED, j)) return false;
                 const int q = (it0 + j) * TILE;
-                tma_reduce_add_4d(&mapdQ, sdO, 0, q, h, b);
-                tma_reduce_add_4d(&mapdQ, sdO + BOX_BYTES, HALF_D, q, h, b);
+                if (a.det_dq) {  // this KV tile's slab of partial dQ; reduce_dq_slabs adds the slabs in a fixed order
+                    tma_store_4d(&mapdQ, sdO, 0, q, h, kt * a.B + b);
+                    tma_store_4d(&mapdQ, sdO + BOX_BYTES, HALF_D, q, h, kt * a.B + b);
+                } else {
+                    tma_reduce_add_4d(&mapdQ, sdO, 0, q, h, b);
+                    tma_reduce_add_4d(&mapdQ, sdO + BOX_BYTES, HALF_D, q, h, b);
+                }
                 bulk_commit_group();
                 bulk_wait_group_read_all();
                 mbar_arrive(&sh.dq_out);

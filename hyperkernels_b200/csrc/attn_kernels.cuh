@@ -52,6 +52,8 @@ struct BwdArgs {
     int causal;
     int accum_dkdv;
     int round_kv;      // 1: K and V arrive unrounded; the compute warps round them to TF32 once they have landed
+    int det_dq;        // 1: dQ tiles are stored (map dQ = the slabs [n_kvtiles * B, H, Tq, 64]) instead of added; B below
+    int B;
     int dropout_mode;
     int drop_scaled;   // 1: inverted dropout; p below is then the softmax over all visible keys
     float dp_scale;    // factor of dP inside dS: scale, times 1/(1-p) when drop_scaled

@@ -208,6 +208,50 @@ int launch_zero_rows(float* ptr, int64_t sB, int64_t sM, int64_t sH, int B, int 
 }
 
 // ---------------------------------------------------------------------------
+// Deterministic dQ: add the per-KV-tile slabs in KV-tile order.  A query tile is in the slab of KV tile kt only if
+// the backward CTA of kt visited it: under the causal mask that is every query tile from
+// it0(kt) = clamp((kt*128 + k_pos0 - q_pos0) / 128) on (attn_bwd_sm100.cu computes the same bound).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) reduce_dq_slabs_kernel(DqReduceJob j, long long nvec) {
+    const long long slab = (long long)j.B * j.H * j.T * 16;  // float4 per slab
+    const int n_qtiles = (j.T + TILE - 1) / TILE;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i >> 4;
+        const int c4 = (int)(i & 15);
+        const int bh = (int)(row / j.T);
+        const int r = (int)(row - (long long)bh * j.T);
+        const int b = bh / j.H, h = bh - b * j.H;
+        const int qt = r / TILE;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4* out = reinterpret_cast<float4*>(j.dQ + (int64_t)b * j.dq_sB + (int64_t)h * j.dq_sH + (int64_t)r * j.dq_sM) + c4;
+        if (j.accumulate) acc = *out;
+        const float4* src = reinterpret_cast<const float4*>(j.slabs) + i;
+        for (int kt = 0; kt < j.n_kvtiles; ++kt) {
+            int it0 = 0;
+            if (j.causal) {
+                const long long first_q = (long long)kt * TILE + j.k_pos0 - j.q_pos0;
+                if (first_q > 0) it0 = (int)min((long long)n_qtiles, first_q / TILE);
+            }
+            if (qt >= it0) {
+                const float4 v = __ldg(src + (long long)kt * slab);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+        }
+        *out = acc;
+    }
+}
+
+int launch_reduce_dq_slabs(const DqReduceJob& j, cudaStream_t stream) {
+    const long long nvec = (long long)j.B * j.H * j.T * 16;
+    if (nvec == 0) return HK_OK;
+    const int blocks = (int)std::min<long long>((nvec + 255) / 256, 148 * 8);
+    reduce_dq_slabs_kernel<<<blocks, 256, 0, stream>>>(j, nvec);
+    count_launch();
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------
 // (O_acc, LSE_acc) <- merge with (O_part, LSE_part): both are normalised
 // softmax outputs over disjoint key sets, so
 //   LSE = log(exp(LSE_a) + exp(LSE_p)),  O = O_a * exp(LSE_a - LSE) + O_p * exp(LSE_p - LSE).

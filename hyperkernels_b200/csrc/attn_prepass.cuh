@@ -28,6 +28,18 @@ int launch_precompute_D_hd(const DJob& j, int head_dim, cudaStream_t stream);
 
 int launch_zero_rows(float* ptr, int64_t sB, int64_t sM, int64_t sH, int B, int H, int T, cudaStream_t stream);
 
+// Deterministic dQ: dQ (+)= sum over KV tiles kt, in increasing kt, of slab[kt][b][h][t][:], skipping the (kt, query
+// tile) pairs the backward kernel never visits (causal mask: query tiles above the diagonal of the KV tile).
+struct DqReduceJob {
+    const float* slabs;  // [n_kvtiles][B][H][T][64] contiguous
+    float* dQ;
+    int64_t dq_sB, dq_sM, dq_sH;
+    int B, H, T, n_kvtiles;
+    int causal, q_pos0, k_pos0;
+    int accumulate;  // 1: add to what dQ holds (HK_FLAG_ACCUM_DQ)
+};
+int launch_reduce_dq_slabs(const DqReduceJob& j, cudaStream_t stream);
+
 int launch_merge_partial(float* O_acc, float* LSE_acc, const float* O_part, const float* LSE_part, long long rows,
                          cudaStream_t stream);
 

@@ -224,12 +224,22 @@ size_t hk_attn_fwd_workspace_bytes(const hk_attn_fwd_params* p) {
     return align_up(bh * p->T * 256, 256) + 2 * align_up(bh * Tk * 256, 256);
 }
 
-size_t hk_attn_bwd_workspace_bytes(const hk_attn_bwd_params* p) {
-    if (!p || (p->flags & HK_FLAG_OPERANDS_PREROUNDED)) return 0;
-    if (p->B <= 0 || p->nh <= 0 || p->T <= 0) return 0;
+// bytes of the rounded operands (Q, dO, K, V) at the head of the backward's workspace
+static size_t bwd_rounded_bytes(const hk_attn_bwd_params* p) {
+    if (p->flags & HK_FLAG_OPERANDS_PREROUNDED) return 0;
     const int64_t Tk = p->kv_len > 0 ? p->kv_len : p->T;
     const size_t bh = (size_t)p->B * p->nh;
-    return 2 * align_up(bh * p->T * 256, 256) + 2 * align_up(bh * Tk * 256, 256);  // Q, dO, K, V
+    return 2 * align_up(bh * p->T * 256, 256) + 2 * align_up(bh * Tk * 256, 256);
+}
+
+size_t hk_attn_bwd_workspace_bytes(const hk_attn_bwd_params* p) {
+    if (!p || p->B <= 0 || p->nh <= 0 || p->T <= 0) return 0;
+    size_t n = bwd_rounded_bytes(p);
+    if (p->flags & HK_FLAG_DETERMINISTIC_DQ) {  // one slab of partial dQ per KV tile
+        const int64_t Tk = p->kv_len > 0 ? p->kv_len : p->T;
+        n += (size_t)((Tk + TILE - 1) / TILE) * align_up((size_t)p->B * p->nh * p->T * 256, 256);
+    }
+    return n;
 }
 
 // 1/(1-p) of the inverted-dropout option, with p as the kernels apply it: the Philox mask drops with
@@ -446,6 +456,16 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     // the tensors the MMAs read: the caller's (pre-rounded) or the rounded copies in the workspace
     View4 tQ = vQ, tK = vK, tV = vV, tdO = vdO;
     bool round_kv = false;
+    const bool det_dq = (p->flags & HK_FLAG_DETERMINISTIC_DQ) != 0;
+    const int n_kvtiles = (int)((Tk + TILE - 1) / TILE);
+    float* dq_slabs = nullptr;
+    if (det_dq) {
+        if ((int64_t)n_kvtiles * B > (1 << 24)) return HK_ERR_BAD_SHAPE;
+        const size_t need = hk_attn_bwd_workspace_bytes(p);
+        if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u))
+            return HK_ERR_WORKSPACE;
+        dq_slabs = reinterpret_cast<float*>(static_cast<uint8_t*>(p->workspace) + bwd_rounded_bytes(p));
+    }
     if (!(p->flags & HK_FLAG_OPERANDS_PREROUNDED)) {
         const size_t need = hk_attn_bwd_workspace_bytes(p);
         if (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u))
@@ -494,7 +514,11 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     if ((rc = make_tile_map(&m.q_mn, tQ.ptr, HEAD_DIM, B, H, Tq, tQ.sB, tQ.sM, tQ.sH, TILE, true))) return rc;
     if ((rc = make_tile_map(&m.k_mn, tK.ptr, HEAD_DIM, B, H, Tk, tK.sB, tK.sM, tK.sH, TILE, true))) return rc;
     if ((rc = make_tile_map(&m.dO_mn, tdO.ptr, HEAD_DIM, B, H, Tq, tdO.sB, tdO.sM, tdO.sH, TILE, true))) return rc;
-    if ((rc = make_tile_map(&m.dQ, p->dQ, HEAD_DIM, B, H, Tq, p->dq_strideB, p->dq_strideM, p->dq_strideH, TILE, false)))
+    if (det_dq) {
+        // the slabs as one tensor [n_kvtiles * B, H, Tq, 64]: KV tile kt of batch b is "batch" kt * B + b
+        if ((rc = make_tile_map(&m.dQ, dq_slabs, HEAD_DIM, n_kvtiles * B, H, Tq, (int64_t)H * Tq * 64, 64, Tq * 64, TILE, false)))
+            return rc;
+    } else if ((rc = make_tile_map(&m.dQ, p->dQ, HEAD_DIM, B, H, Tq, p->dq_strideB, p->dq_strideM, p->dq_strideH, TILE, false)))
         return rc;
     if ((rc = make_tile_map(&m.dK, p->dK, HEAD_DIM, B, H, Tk, p->dk_strideB, p->dk_strideM, p->dk_strideH, TILE, false)))
         return rc;
@@ -505,12 +529,12 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
         j.dO = vdO; j.O = vO;
         j.D = p->D; j.d_sB = p->d_strideB; j.d_sH = p->d_strideH;
         j.dO_rounded = dO_rounded;
-        if (!(p->flags & HK_FLAG_ACCUM_DQ)) {
+        if (!(p->flags & HK_FLAG_ACCUM_DQ) && !det_dq) {  // the slab reduction overwrites dQ
             j.dQ_zero = p->dQ; j.dq_sB = p->dq_strideB; j.dq_sM = p->dq_strideM; j.dq_sH = p->dq_strideH;
         }
         j.H = H; j.BH = BH; j.T = (int)Tq;
         if ((rc = launch_precompute_D(j, stream))) return rc;
-    } else if (!(p->flags & HK_FLAG_ACCUM_DQ)) {
+    } else if (!(p->flags & HK_FLAG_ACCUM_DQ) && !det_dq) {
         if ((rc = launch_zero_rows(p->dQ, p->dq_strideB, p->dq_strideM, p->dq_strideH, B, H, (int)Tq, stream))) return rc;
     }
 
@@ -522,7 +546,9 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     a.dk_sB = p->dk_strideB; a.dk_sM = p->dk_strideM; a.dk_sH = p->dk_strideH;
     a.dv_sB = p->dv_strideB; a.dv_sM = p->dv_strideM; a.dv_sH = p->dv_strideH;
     a.H = H; a.BH = BH; a.Tq = (int)Tq; a.Tk = (int)Tk;
-    a.n_kvtiles = (int)((Tk + TILE - 1) / TILE);
+    a.n_kvtiles = n_kvtiles;
+    a.det_dq = det_dq ? 1 : 0;
+    a.B = B;
     a.q_pos0 = (int)p->q_pos0; a.k_pos0 = (int)p->k_pos0;
     a.scale = p->scale; a.scale_log2e = p->scale * LOG2E;
     a.causal = p->is_causal ? 1 : 0;
@@ -538,7 +564,17 @@ int hk_attn_backward(const hk_attn_bwd_params* p, void* stream_) {
     if (!a.status) return HK_ERR_CUDA;
     a.timeline = g_timeline.load();
     a.timeline_block = g_timeline_block.load();
-    return launch_attn_bwd(m, a, stream);
+    if ((rc = launch_attn_bwd(m, a, stream))) return rc;
+    if (det_dq) {
+        DqReduceJob r{};
+        r.slabs = dq_slabs; r.dQ = p->dQ;
+        r.dq_sB = p->dq_strideB; r.dq_sM = p->dq_strideM; r.dq_sH = p->dq_strideH;
+        r.B = B; r.H = H; r.T = (int)Tq; r.n_kvtiles = n_kvtiles;
+        r.causal = a.causal; r.q_pos0 = a.q_pos0; r.k_pos0 = a.k_pos0;
+        r.accumulate = (p->flags & HK_FLAG_ACCUM_DQ) ? 1 : 0;
+        return launch_reduce_dq_slabs(r, stream);
+    }
+    return HK_OK;
 }
 
 int hk_attn_merge_partial(float* O_acc, float* LSE_acc, const float* O_part, const float* LSE_part, int64_t rows,

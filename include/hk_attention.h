@@ -96,7 +96,14 @@ enum {
      * the rounded tensors for a backward with HK_FLAG_REUSE_FWD_ROUNDED); stand-alone backward: K and V (Q and dO
      * are still rounded into the workspace) -- because there the pre-pass costs more than the extra
      * shared-memory traffic; both ways give the same bits. */
-    HK_FLAG_ROUND_IN_HBM = 1u << 8
+    HK_FLAG_ROUND_IN_HBM = 1u << 8,
+    /* backward: deterministic dQ.  By default the KV-tile CTAs add their dQ tiles into dQ with bulk reductions whose
+     * order is not fixed (run-to-run differences of the order of 1e-5); with this flag every CTA stores its tiles
+     * into the workspace instead (ceil(kv_len / 128) slabs of B*nh*T*256 bytes behind the rounded operands:
+     * hk_attn_bwd_workspace_bytes counts them) and a second kernel adds the slabs in KV-tile order: the same
+     * inputs give the same bits on every run.  The reference's own dQ is accumulated with atomicAdd
+     * (mem_efficient_bwd_unified_kernel_exp12.cu:239-260) and is not reproducible either. */
+    HK_FLAG_DETERMINISTIC_DQ = 1u << 9
 };
 
 /* ---- forward ------------------------------------------------------------

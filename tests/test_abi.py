@@ -139,6 +139,12 @@ def test_workspace_sizes():
             assert hk.fwd_workspace_bytes(p) == 3 * 2 * 3 * T * 256
     b = BP(); b.B, b.nh, b.T = 2, 3, 100
     assert hk.bwd_workspace_bytes(b) == 4 * 2 * 3 * 100 * 256
+    # deterministic dQ: one slab of B*nh*T*256 bytes per 128-key tile behind the rounded operands (alone if those are skipped)
+    b.T, b.kv_len = 300, 500
+    b.flags = hk.FLAG_DETERMINISTIC_DQ
+    assert hk.bwd_workspace_bytes(b) == 2 * 3 * 256 * (2 * 300 + 2 * 500) + 4 * (2 * 3 * 300 * 256)
+    b.flags = hk.FLAG_DETERMINISTIC_DQ | hk.FLAG_OPERANDS_PREROUNDED
+    assert hk.bwd_workspace_bytes(b) == 4 * (2 * 3 * 300 * 256)
 
 
 def test_status_strings_and_counters():

@@ -632,6 +632,37 @@ def test_random_shapes_the_two_rounding_paths_and_the_workspace_hand_over_agree(
         assert bool(torch.isfinite(O2).all()), what
 
 
+@pytest.mark.parametrize("Tq,Tk,causal,q_pos0", [(333, 333, 1, 0), (640, 640, 0, 0), (200, 384, 1, 184), (1024, 1024, 1, 0)])
+def test_deterministic_dq_is_bit_reproducible_and_equal_to_the_default(Tq, Tk, causal, q_pos0):
+    """HK_FLAG_DETERMINISTIC_DQ: every KV-tile CTA stores its dQ tiles into a slab of the workspace and a second kernel
+    adds the slabs in KV-tile order.  Same inputs, same bits, run after run (the default path adds with bulk reductions
+    in whatever order the CTAs finish); the values agree with the default path and pass the oracle gate; accumulation
+    into a given dQ works as on the default path."""
+    B, H = 2, 3
+    Q, dO = normal((B, H, Tq, 64), 920), normal((B, H, Tq, 64), 921)
+    K, V = normal((B, H, Tk, 64), 922), normal((B, H, Tk, 64), 923)
+    O_ref, L_ref = ol.attn_forward_mt(Q, K, V, SCALE, causal, None, q_pos0, 0)
+    _, dQ_ref, dK_ref, dV_ref = ol.attn_backward_mt(Q, K, V, O_ref, dO, L_ref, SCALE, causal, None, q_pos0, 0)
+    tQ, tK, tV, tdO, tO, tL = dev(Q), dev(K), dev(V), dev(dO), dev(O_ref), dev(L_ref)
+    runs = [hk.attention_backward(tQ, tK, tV, tO, tdO, tL, SCALE, causal, q_pos0=q_pos0, deterministic_dq=True)
+            for _ in range(4)]
+    ok_status()
+    for r in runs[1:]:
+        assert torch.equal(r[0], runs[0][0]) and torch.equal(r[1], runs[0][1]) and torch.equal(r[2], runs[0][2])
+    gate("dQ", host(runs[0][0]), dQ_ref)
+    gate("dK", host(runs[0][1]), dK_ref)
+    gate("dV", host(runs[0][2]), dV_ref)
+    dflt = hk.attention_backward(tQ, tK, tV, tO, tdO, tL, SCALE, causal, q_pos0=q_pos0)
+    assert float((dflt[0] - runs[0][0]).abs().max()) <= 1e-4
+    assert torch.equal(dflt[1], runs[0][1]) and torch.equal(dflt[2], runs[0][2])
+    # accumulation into a given dQ
+    base = dev(normal((B, H, Tq, 64), 924))
+    acc = base.clone()
+    hk.attention_backward(tQ, tK, tV, tO, tdO, tL, SCALE, causal, q_pos0=q_pos0, deterministic_dq=True, accum_dq=True, dQ=acc)
+    ok_status()
+    assert float((acc - (base + runs[0][0])).abs().max()) <= 1e-5  # (base + slab0) + slab1 ... against base + (sum of slabs)
+
+
 def test_graphed_step_replays_the_direct_calls():
     """GraphedAttentionStep (forward + backward captured in a CUDA graph): a replay gives what the direct calls give,
     also after the inputs were refilled in place."""
