@@ -663,6 +663,47 @@ def test_deterministic_dq_is_bit_reproducible_and_equal_to_the_default(Tq, Tk, c
     assert float((acc - (base + runs[0][0])).abs().max()) <= 1e-5  # (base + slab0) + slab1 ... against base + (sum of slabs)
 
 
+@pytest.mark.parametrize("T,causal", [(333, 1), (129, 0), (640, 1), (1000, 0)])
+def test_outputs_stay_inside_their_buffers(T, causal):
+    """Canary bands round every output (the memory checker is closed on this pool): O, LSE, dQ, dK, dV and D are views
+    into one sentinel-filled allocation with 64 KiB of guard on both sides of each; after a forward and a backward on
+    a ragged shape -- whose last tiles the TMA stores must clip -- every guard byte still holds the sentinel, and so
+    does the workspace beyond the bytes the library asked for."""
+    B, H = 2, 3
+    Q, K, V, dO = (dev(normal((B, H, T, 64), 930 + s)) for s in range(4))
+    guard = 16384  # floats
+    n_big, n_small = B * H * T * 64, B * H * T
+    sizes = [n_big, n_small, n_big, n_big, n_big, n_small]  # O, LSE, dQ, dK, dV, D
+    pad = lambda x: (x + 63) // 64 * 64  # keeps every view 256-byte aligned; the padding belongs to the guard
+    total = guard + sum(pad(x) + guard for x in sizes)
+    SENT = 12345.678
+    arena = torch.full((total,), SENT, dtype=torch.float32, device="cuda")
+    views, off = [], guard
+    for x in sizes:
+        views.append(arena[off:off + x])
+        off += pad(x) + guard
+    O, LSE, dQ, dK, dV, D = views
+    O, dQ, dK, dV = (t.view(B, H, T, 64) for t in (O, dQ, dK, dV))
+    LSE, D = LSE.view(B, H, T), D.view(B, H, T)
+    p = hk.MemEfficientBwdParams()
+    p.B, p.nh, p.T = B, H, T
+    need = hk.bwd_workspace_bytes(p)
+    ws = torch.full((need + 256 + 65536,), 0x5A, dtype=torch.uint8, device="cuda")
+    hk.attention_forward(Q, K, V, SCALE, causal, out=O, lse=LSE, workspace=ws[:need + 256])
+    hk.attention_backward(Q, K, V, O, dO, LSE, SCALE, causal, D=D, dQ=dQ, dK=dK, dV=dV, workspace=ws[:need + 256],
+                          reuse_fwd_rounded=True)
+    ok_status()
+    mask = torch.ones(total, dtype=torch.bool, device="cuda")
+    off = guard
+    for x in sizes:
+        mask[off:off + x] = False
+        off += pad(x) + guard
+    assert bool((arena[mask] == SENT).all()), "a guard band was written"
+    assert bool((ws[need + 256:] == 0x5A).all()), "the workspace was written past the size the library asked for"
+    for t in (O, dQ, dK, dV, LSE, D):
+        assert bool(torch.isfinite(t).all()) and not bool((t == SENT).all())
+
+
 def test_graphed_step_replays_the_direct_calls():
     """GraphedAttentionStep (forward + backward captured in a CUDA graph): a replay gives what the direct calls give,
     also after the inputs were refilled in place."""
