@@ -523,6 +523,26 @@ def strong_cfg4(args, rank, world, dist, flush, stream):
             "efficiency": ms1 / (world * ms), "collective": "none", "timing": "median of 15 graph replays, max over ranks"}
 
 
+def _captured_ring_step(ring, Q, K, V, dO, eager_step, dist, torch):
+    """The ring step as one CUDA-graph launch per rank (hyperkernels_b200.ring.GraphedRingStep) if every rank could
+    capture it, else the call-by-call step on every rank."""
+    from hyperkernels_b200.ring import GraphedRingStep
+
+    gs, ok = None, 1
+    try:
+        if os.environ.get("HK_BENCH_RING_EAGER"):  # for comparison runs
+            raise RuntimeError("HK_BENCH_RING_EAGER is set")
+        gs = GraphedRingStep(ring, Q, K, V, dO)
+    except Exception as e:  # capture is all-or-nothing over the ranks: NCCL operations must match
+        print(f"bench: ring step not captured ({e}); issuing it call by call", file=sys.stderr)
+        ok = 0
+    flag = torch.tensor([ok], device="cuda", dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) == 1:
+        return gs.replay, "one CUDA-graph launch per rank and step (kernels, NCCL hops and their ordering captured)"
+    return eager_step, "call by call from Python"
+
+
 def ring_cfg5(args, rank, local_rank, world, dist, flush, stream, Gs=2):
     """Config 5 (B=1, H=32, N=32768, causal, every 64th key x8): heads split over world/Gs groups, the sequence of each
     group sharded over a Gs-rank KV ring (zigzag chunks, NCCL send/recv on a side stream under the compute)."""
@@ -560,8 +580,14 @@ def ring_cfg5(args, rank, local_rank, world, dist, flush, stream, Gs=2):
     torch.cuda.synchronize()
     dist.barrier()
     n0 = hk.launch_count()
-    samples = timed_samples(step, 8, flush, stream, torch)
-    launches = (hk.launch_count() - n0) // 8
+    step()
+    launches = hk.launch_count() - n0
+    run, how = _captured_ring_step(ring, Q, K, V, dO, step, dist, torch)
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    dist.barrier()
+    samples = timed_samples(run, 8, flush, stream, torch)
     ms = _median(samples)
     # second pass with the library's kernel events on: how much of the step the two tensor-core kernels are busy
     L.hk_attn_kernel_timing_enable(1)
@@ -580,6 +606,7 @@ def ring_cfg5(args, rank, local_rank, world, dist, flush, stream, Gs=2):
             "value": flops(full) / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
             "single_gpu_ms_per_step": ms1, "single_gpu_value": flops(full) / (ms1 * 1e-3) / 1e12,
             "efficiency": ms1 / (world * ms), "kernels_busy_frac": busy / ms, "launches_per_step": int(launches),
+            "issue": how,
             "collective": "NCCL send/recv of K/V blocks and of the travelling dK/dV accumulators, one hop per ring step",
             "timing": "median of 8 steps (CUDA events), max over ranks"}
 
@@ -636,15 +663,19 @@ def run_ours_ring(args, cfg, rank, local_rank, world):
     clocks = ClockSampler(local_rank)
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     n0 = hk.launch_count()
+    step()
+    launches = (hk.launch_count() - n0) * args.steps
+    run, how = _captured_ring_step(ring, Q, K, V, dO, step, dist, torch)
+    for _ in range(2):
+        run()
     barrier()
     clocks.start()
     for a, b in ev:
         flush.zero_()
         a.record(stream)
-        step()
+        run()
         b.record(stream)
     barrier()
-    launches = hk.launch_count() - n0
     ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps
     # second, untimed pass with the library's kernel events on (they cost two event creations per launch, which do
     # not belong in the timed region): how long the two tensor-core kernels run per step
@@ -692,7 +723,8 @@ def run_ours_ring(args, cfg, rank, local_rank, world):
             "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
             "config": {"workload": cfg["name"], "config_id": args.config, "mesh": f"{Gh} head groups x {Gs}-rank KV ring (zigzag)",
                        "l2": "256 MiB buffer written between timed steps (untimed)",
-                       "step": "ring forward + ring backward (hk_attn_forward/backward per segment pair, NCCL send/recv)"},
+                       "step": "ring forward + ring backward (hk_attn_forward/backward per segment pair, NCCL send/recv)",
+                       "issue": how},
             "pct_of_tf32_peak": total / world / (ms * 1e-3) / 1e12 / peaks["tf32_tflops"],
             "kernel_ms": {"fwd_kernels_per_step": kt["fwd"], "bwd_kernels_per_step": kt["bwd"]},
             "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel", "achieved": achieved, "peak": peaks["tf32_tflops"],

@@ -339,3 +339,42 @@ class RingAttention:
             acc_handle = self._start_exchange(part, acc_in)  # t < G-1: to the next worker; t = G-1: the hop home
         self._finish(acc_handle)
         return dQ, acc_in[0].clone(), acc_in[1].clone()
+
+
+class GraphedRingStep:
+    """One forward + backward of a RingAttention on fixed shard tensors, captured in a CUDA graph and replayed.
+
+    Every launch, every hop (ncclSend/ncclRecv through the native transport) and the event ordering between the
+    compute and the communication stream are recorded once; a step is then one graph launch per rank, with no host work
+    between the hops.  All ranks of the ring must construct it, and replay it, the same number of times.  The shard
+    tensors are read in place at every replay (refill them to change the inputs); the results are the attributes
+    O, LSE, dQ, dK, dV.  Needs the native transport (NCCL operations issued through torch.distributed are not captured
+    here) and a ring without a host-side timeout (a host wait cannot be captured)."""
+
+    def __init__(self, ring: RingAttention, Q, K, V, dO):
+        if ring.world > 1 and ring.native is None:
+            raise RingError("a captured ring step needs the native transport")
+        if ring.timeout_s is not None:
+            raise RingError("a captured ring step cannot wait on the host: construct the ring without timeout_s")
+        self.ring = ring
+        self._in = (Q, K, V, dO)
+        self.O = self.LSE = self.dQ = self.dK = self.dV = None
+
+        def step():
+            self.O, self.LSE = ring.forward(Q, K, V)
+            self.dQ, self.dK, self.dV = ring.backward(Q, K, V, self.O, self.LSE, dO)
+
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            step()  # eager once: buffers, first-call set-up of the kernels and of NCCL's connections
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                step()
+        cur.wait_stream(side)
+
+    def replay(self) -> None:
+        """Enqueue one step on the current stream."""
+        self.graph.replay()

@@ -132,3 +132,60 @@ def test_native_hop_that_never_completes_raises_ring_error():
         assert p.exitcode == 0
     assert results[0].startswith("RingError") and "did not complete in time" in results[0], results
     assert results[1] == "idle"
+
+
+def _graph_worker(rank, world, port, ret):
+    """The captured ring step (GraphedRingStep) gives what the call-by-call ring gives, also after the inputs were
+    refilled in place; every rank replays the same number of times."""
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import hyperkernels_b200 as hk
+        from hyperkernels_b200.ring import GraphedRingStep, RingAttention
+
+        T, B, H = 2048, 1, 4
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)
+        Q, K, V, dO = (torch.randn((B, H, T // world, 64), generator=g, device="cuda") for _ in range(4))
+        ring = RingAttention(T, 0.125, True, layout="zigzag")
+        gs = GraphedRingStep(ring, Q, K, V, dO)
+        worst = 0.0
+        for it in range(3):
+            if it:
+                for t in (Q, K, V, dO):
+                    t.copy_(torch.randn(t.shape, generator=g, device="cuda"))
+            gs.replay()
+            torch.cuda.synchronize()
+            O, LSE = ring.forward(Q, K, V)
+            dQ, dK, dV = ring.backward(Q, K, V, O, LSE, dO)
+            torch.cuda.synchronize()
+            assert hk.last_device_status() == 0
+            assert torch.equal(gs.O, O) and torch.equal(gs.LSE, LSE), it
+            assert torch.equal(gs.dK, dK) and torch.equal(gs.dV, dV), it
+            worst = max(worst, float((gs.dQ - dQ).abs().max()))
+        ret.put((rank, worst))
+        ret.close()
+        ret.join_thread()
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_captured_ring_step_equals_the_call_by_call_ring():
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_graph_worker, args=(r, world, 29891, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(ret.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(w <= 1e-4 for w in results.values()), results
