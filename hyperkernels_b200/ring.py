@@ -14,7 +14,8 @@ pair, told where the two segments sit in the global sequence
 the starting state of the next call (``HK_FLAG_CONTINUE_SOFTMAX_STATE``), so no
 partial outputs and no merge kernel exist; in the backward each rank computes its
 contribution to the gradient of the visiting K/V block and adds it to an
-accumulator that travels one step behind the block.  Every buffer a step needs
+accumulator that travels one step behind the block (its hop runs under the
+kernels of the next step; the arriving sum is added after them).  Every buffer a step needs
 (two K/V message buffers, the gradient accumulators, the rounded shards) is
 allocated once per shape and reused.
 
@@ -315,14 +316,11 @@ class RingAttention:
                 kv_handle = self._start_exchange(kv, nxt)
             k_views = self._seg_views(kv[0], src_segs)
             v_views = self._seg_views(kv[1], src_segs)
-            # this rank's (dK, dV) contribution to the visiting block, on top of what the block has collected so
-            # far: the accumulator that left the previous rank one step ago
+            # this rank's (dK, dV) contribution to the visiting block; what the block has collected so far -- the
+            # accumulator that left the previous rank one step ago -- is added after the kernels, so that its hop
+            # runs under them instead of in front of them
             part = buf["acc"][t & 1]
-            if t > 0:
-                self._finish(acc_handle)
-                part.copy_(acc_in)
-            else:
-                part.zero_()
+            part.zero_()
             pk_views = self._seg_views(part[0], src_segs)
             pv_views = self._seg_views(part[1], src_segs)
             for qi, qseg in enumerate(self.my_segs):
@@ -331,6 +329,9 @@ class RingAttention:
                         self.backend.bwd(q_views[qi], k_views[ki], v_views[ki], o_views[qi], do_views[qi], lse_views[qi],
                                          d_views[qi], self.scale, self.causal, qseg[0], kseg[0], dq_views[qi],
                                          pk_views[ki], pv_views[ki])
+            if t > 0:
+                self._finish(acc_handle)
+                part.add_(acc_in)
             if kv_handle is not None:
                 self._finish(kv_handle)
                 kv = nxt
