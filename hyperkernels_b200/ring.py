@@ -179,7 +179,10 @@ class RingAttention:
         self.T, self.scale, self.causal, self.layout = T, scale, causal, layout
         self.backend = backend if backend is not None else CudaBackend()
         self.my_segs = segments_of(self.rank, self.world, T, layout)
-        self.comm_stream = torch.cuda.Stream() if torch.cuda.is_available() and backend is None else None
+        # The hops run on a HIGH-PRIORITY stream: an attention kernel fills every SM (one CTA takes the whole register
+        # file), so the CTAs of an NCCL kernel launched behind it would otherwise wait for its last wave; with priority
+        # they take the first SM that frees up and the hop really runs under the kernels.
+        self.comm_stream = (torch.cuda.Stream(priority=-1) if torch.cuda.is_available() and backend is None else None)
         if transport == "auto":
             transport = "native" if (self.comm_stream is not None and self.world > 1) else "torch"
         self.native = NativeTransport(group, self.rank, self.world) if transport == "native" else None
