@@ -1,7 +1,7 @@
 // umma_rate.cu -- TEST INFRASTRUCTURE: how fast one warp can feed tcgen05.mma.kind::tf32.
 //
 // The attention kernels rest on two measured facts about the sm_100a tensor pipe, and this probe re-measures them so
-// that tests/test_mma_rates_gpu.py can hold them (and profiles/tf32_mma_peak_probe.md can be regenerated):
+// that tests/test_mma_rates_gpu.py can hold them:
 //   1. a tcgen05.mma issued from inside a divergent `if (lane == 0)` region costs the issuing thread ~50 cycles, more
 //      than an M128 N64 K8 product takes (36): issued by a converged warp with only the instruction predicated on the
 //      elected lane, the same products run at the tensor pipe's own rate;

@@ -7,7 +7,7 @@ are held here because the kernels' structure depends on them:
   `if (lane == 0)` region -- the kernels issue the first way;
 * M64 shapes run at half the M128 rate, so splitting a tile into two M64 products buys nothing.
 
-Run with `-s` to print the whole table (the figures quoted in profiles/tf32_mma_peak_probe.md).
+Run with `-s` to print the whole table (shape, issue style, TFLOP/s, cycles per instruction).
 """
 import ctypes
 import os
