@@ -226,7 +226,11 @@ int hk_attn_bwd_precompute_D_hd(const hk_attn_bwd_params* p, int head_dim, void*
  * Writes dQ, dK, dV (and D). */
 int hk_attn_backward(const hk_attn_bwd_params* p, void* stream);
 
-/* Scratch the two calls need for the given block (0 when none). */
+/* Scratch the two calls need for the given block, flags included (0 when none).  Forward: the rounded Q, K, V
+ * (3 tensors) when the HBM pre-pass rounds them, nothing when the kernel rounds in shared memory -- though a workspace
+ * of hk_attn_bwd_workspace_bytes given to it then receives the rounded tensors for HK_FLAG_REUSE_FWD_ROUNDED.
+ * Backward: the rounded Q, K, V, dO (4 tensors, in the forward's order followed by dO), then, with
+ * HK_FLAG_DETERMINISTIC_DQ, one slab of partial dQ per 128-key tile. */
 size_t hk_attn_fwd_workspace_bytes(const hk_attn_fwd_params* p);
 size_t hk_attn_bwd_workspace_bytes(const hk_attn_bwd_params* p);
 
