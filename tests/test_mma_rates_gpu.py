@@ -88,7 +88,7 @@ def test_issue_from_a_converged_warp_and_shape_costs(probe):
             print(f"{name:<66} {'converged' if conv else 'lane-0 if':<10} {tf:8.1f} {cyc:10.1f} {mhz:7d}")
     # the N64 products and the tile mix are issue-bound from a divergent region
     assert rows[(1, 1)][1] > 1.15 * rows[(1, 0)][1]
-    assert rows[(6, 1)][1] > 1.04 * rows[(6, 0)][1]
+    assert rows[(6, 1)][1] > 1.02 * rows[(6, 0)][1]
     # M64 runs at half rate: no more than 0.6 of the M128 throughput at the same N
     assert rows[(3, 1)][1] < 0.6 * rows[(0, 1)][1]
     assert rows[(4, 1)][1] < 0.6 * rows[(5, 1)][1]
