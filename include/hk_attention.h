@@ -101,7 +101,9 @@ enum {
      * order is not fixed (run-to-run differences of the order of 1e-5); with this flag every CTA stores its tiles
      * into the workspace instead (ceil(kv_len / 128) slabs of B*nh*T*256 bytes behind the rounded operands:
      * hk_attn_bwd_workspace_bytes counts them) and a second kernel adds the slabs in KV-tile order: the same
-     * inputs give the same bits on every run.  The reference's own dQ is accumulated with atomicAdd
+     * inputs give the same bits on every run.  The slabs are ceil(kv_len / 128) times the size of dQ: meant for
+     * the sequence lengths of training batches, not for a 32k-token single sequence.  The reference's own dQ is
+     * accumulated with atomicAdd
      * (mem_efficient_bwd_unified_kernel_exp12.cu:239-260) and is not reproducible either. */
     HK_FLAG_DETERMINISTIC_DQ = 1u << 9
 };
